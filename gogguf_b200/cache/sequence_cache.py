@@ -7,6 +7,9 @@ What each scheduled layer needs is asked of its mixer as a *request*:
   its own: pools ``k, v [layer_in_group][page][kv_head][page_size][head_dim]`` and, per slot, the
   list of pages that hold its positions.  A windowed group gives pages back as soon as every
   position in them has left the window.
+* `LatentRequest(width, window)` - one vector per position (latent attention caches its compressed
+  key/value vector and the shared rotated key part instead of per-head keys and values); paged and
+  windowed like the above, pool ``[layer_in_group][page][page_size][width]``.
 * `StateRequest(shape, dtype)` - a fixed-size state per sequence, ``[max_slots, *shape]`` for that
   layer, zeroed when a slot is opened.
 * None - the layer keeps nothing.
@@ -229,6 +232,44 @@ class KVView:
     v: torch.Tensor
     page_size: int
     request: KVRequest
+
+
+@dataclass(frozen=True)
+class LatentRequest:
+    """One vector of `width` elements per position (a compressed key/value latent with whatever rides beside
+    it), of which a layer reads the last `window` positions (None: all)."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass
+class LatentView:
+    """What a latent-attention mixer gets for one scheduled layer: its slice of the store's pool."""
+    group: int
+    pool: torch.Tensor         # [page][page_size][width]
+    page_size: int
+    request: LatentRequest
+
+
+@register_cache_store(LatentRequest)
+class LatentStore(PagedStore):
+    """Storage of the layers that share one `LatentRequest`: ``pool [layer][page][page_size][width]``.  Rows are
+    padded to a multiple of 8 elements so that every position starts on a 16-byte boundary in bfloat16."""
+
+    @staticmethod
+    def group_key(request: LatentRequest):
+        return request
+
+    def __init__(self, request: LatentRequest, entries: List[int], n_pages: int, page_size: int,
+                 dtype: torch.dtype, device, max_slots: int = 0):
+        super().__init__(request, entries, n_pages, page_size, window=request.window)
+        self.row = (request.width + 7) // 8 * 8
+        # zero-filled once: a page that is handed out again holds old finite numbers, never NaN patterns
+        self.pool = torch.zeros((len(entries), n_pages, page_size, self.row), dtype=dtype, device=device)
+
+    def view(self, entry: int) -> LatentView:
+        li = self.entries.index(entry)
+        return LatentView(group=self.index, pool=self.pool[li], page_size=self.page_size, request=self.request)
 
 
 @dataclass

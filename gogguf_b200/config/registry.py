@@ -3,7 +3,7 @@
 The reference dispatches on ``general.architecture`` with a switch and fails
 on unknown names (pkg/model/model.go:23-48).  Here the dispatch is a table so
 that an architecture is added by one `register_architecture` call; the key is
-``architectures[0]`` of config.json, with ``model_type`` as an alias.
+``architectures[0]`` (or the string ``architecture``) of config.json, with ``model_type`` as an alias.
 """
 from __future__ import annotations
 
@@ -43,9 +43,11 @@ def architecture_name(cfg: Dict[str, Any]) -> str:
     archs = cfg.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         return str(archs[0])
+    if isinstance(cfg.get("architecture"), str):
+        return cfg["architecture"]
     if "model_type" in cfg:
         return str(cfg["model_type"])
-    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+    raise ConfigError("config.json names no architecture (none of 'architectures', 'architecture', 'model_type')")
 
 
 def config_class_for(name: str) -> Type:

@@ -59,8 +59,10 @@ class BlockSpec:
 
     arrangement: str  # registry key of the block arrangement, e.g. "pre_norm"
     parts: Mapping[str, PartSpec]
+    params: Mapping[str, Any]      # constants of the arrangement itself (a factor on what the block adds, ...)
 
-    def __init__(self, arrangement: str, parts: Optional[Mapping[str, PartSpec]] = None, **roles: PartSpec):
+    def __init__(self, arrangement: str, parts: Optional[Mapping[str, PartSpec]] = None,
+                 params: Optional[Mapping[str, Any]] = None, **roles: PartSpec):
         merged = dict(parts or {})
         for role, ps in roles.items():
             if role in merged:
@@ -71,6 +73,7 @@ class BlockSpec:
                 raise TypeError(f"block spec: role {role!r} must be a PartSpec, got {type(ps).__name__}")
         object.__setattr__(self, "arrangement", arrangement)
         object.__setattr__(self, "parts", MappingProxyType(merged))
+        object.__setattr__(self, "params", MappingProxyType(dict(params or {})))
 
     def __getattr__(self, role: str) -> PartSpec:
         # only reached when normal lookup fails: a role read as an attribute
@@ -86,10 +89,10 @@ class BlockSpec:
             merged.pop(role, None)
         else:
             merged[role] = part
-        return BlockSpec(self.arrangement, merged)
+        return BlockSpec(self.arrangement, merged, params=dict(self.params))
 
     def with_arrangement(self, arrangement: str) -> "BlockSpec":
-        return BlockSpec(arrangement, dict(self.parts))
+        return BlockSpec(arrangement, dict(self.parts), params=dict(self.params))
 
 
 @dataclass(frozen=True)

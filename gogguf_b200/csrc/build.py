@@ -54,6 +54,8 @@ MODULES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "gemm_plain": "gemm_plain.cu",
     "attention_plain": "attention_plain.cu",
+    "latent_attention": "latent_attention.cu",
+    "moe": "moe.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",

@@ -464,6 +464,46 @@ GG_API gg_residual_add(float* x, const void* delta, int dtype, long long n, cuda
     return gg_last_error();
 }
 
+// x (float32) += alpha * delta: what an arrangement with a factor on its parts' outputs adds when a part
+// could not take the factor into its own last product.
+template <typename T>
+__global__ void residual_axpy_kernel(float* __restrict__ x, const T* delta, float alpha, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) x[idx] = fmaf(alpha, to_f<T>(delta[idx]), x[idx]);
+}
+
+GG_API gg_residual_axpy(float* x, const void* delta, int dtype, float alpha, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(residual_axpy_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, x, (const T*)delta, alpha, n));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- xIELU
+// out = out_scale * f(z), f(z) = ap z^2 + z / 2 for z > 0 and aq (exp(z) - 1 - z) + z / 2 otherwise; ap and aq are
+// the activation's two coefficients as the host derived them from its stored scalars (ap = softplus(p),
+// aq = 1/2 + softplus(q)).  float32 arithmetic; expm1f keeps exp(z) - 1 exact near zero.
+template <typename T>
+__global__ void xielu_kernel(const T* z, T* out, float ap, float aq, float out_scale, long long n) {
+    pdl_launch();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float v = to_f<T>(z[idx]);
+    const float f = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(aq, expm1f(v) - v, 0.5f * v);
+    out[idx] = from_f<T>(f * out_scale);
+}
+
+GG_API gg_xielu(const void* z, int dtype, void* out, float ap, float aq, float out_scale, long long n,
+                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    GG_DISPATCH_DTYPE(dtype, T,
+        gg_launch(xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const T*)z, (T*)out, ap, aq, out_scale, n));
+    return gg_last_error();
+}
+
 // ----------------------------------------------------------------------------- token feed
 // tokens[i] = sampled[src[i]] where src[i] >= 0: lets a decode step take the ids that the previous
 // step's sampling kernel left on the device, without a round trip through the host.

@@ -116,6 +116,22 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     kernel("elementwise", "gg_residual_add")(_p(x), _p(delta), dtype_code(delta.dtype), x.numel(), _stream())
 
 
+def residual_axpy(x: torch.Tensor, delta: torch.Tensor, alpha: float) -> None:
+    """x (float32) += alpha * delta."""
+    _need(x, torch.float32, "x")
+    if delta.numel() != x.numel() or not delta.is_contiguous():
+        raise KernelError("residual_axpy: shapes disagree")
+    kernel("elementwise", "gg_residual_axpy")(_p(x), _p(delta), dtype_code(delta.dtype), float(alpha), x.numel(), _stream())
+
+
+def xielu(z: torch.Tensor, out: torch.Tensor, ap: float, aq: float, out_scale: float = 1.0) -> None:
+    """out = out_scale * (ap z^2 + z/2 where z > 0, aq (exp(z) - 1 - z) + z/2 elsewhere), float32 arithmetic."""
+    if z.dtype != out.dtype or z.numel() != out.numel() or not z.is_contiguous() or not out.is_contiguous():
+        raise KernelError("xielu: input and output must be contiguous and alike")
+    kernel("elementwise", "gg_xielu")(_p(z), dtype_code(z.dtype), _p(out), float(ap), float(aq), float(out_scale),
+                                       z.numel(), _stream())
+
+
 def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor, n: int) -> None:
     """tokens[i] = sampled[src[i]] where src[i] >= 0 (all int32, on the device)."""
     _need(tokens, torch.int32, "tokens")
@@ -150,6 +166,82 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token),
         _p(page_table), page_table.shape[-1], page_size, k_pool.shape[0], n_tokens, nq, nkv, d, float(scale),
         int(window), _p(status_word(q.device)), _stream())
+
+
+# ------------------------------------------------------------------------------- latent attention
+def latent_prep(q: torch.Tensor, dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos: torch.Tensor,
+                sin: torch.Tensor, rot_dims: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                page_table: torch.Tensor, page_size: int, pool: Optional[torch.Tensor], qcat: torch.Tensor,
+                n_tokens: int, heads: int, d: int, r: int, R: int) -> None:
+    """Norm of the latent, rotation of the shared key part and of the queries' rotated parts, cache write.
+    q [T, heads * (d + r)] and dkv [T, R + r] may be column ranges of one buffer (row strides are passed);
+    pool [page][page_size][row]; qcat [T, heads, R + r] receives the rotated parts at [..., R:]."""
+    if q.dtype != dkv.dtype or (pool is not None and pool.dtype != q.dtype):
+        raise KernelError("latent_prep: q, dkv and the cache must share one dtype")
+    if q.stride(-1) != 1 or dkv.stride(-1) != 1 or not qcat.is_contiguous():
+        raise KernelError("latent_prep: rows must be contiguous")
+    _need(norm_weight, torch.float32, "norm weight")
+    from .tcgen05_gemm import status_word
+    kernel("latent_attention", "gg_latent_prep")(
+        _p(q), q.stride(0), _p(dkv), dkv.stride(0), dtype_code(q.dtype), _p(norm_weight), float(eps), _p(cos), _p(sin),
+        int(rot_dims), _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], int(page_size),
+        pool.shape[0] if pool is not None else 0, _p(pool), pool.shape[-1] if pool is not None else R + r,
+        _p(qcat), dtype_code(qcat.dtype), n_tokens, heads, d, r, R, _p(status_word(q.device)), _stream())
+
+
+def headwise_gemm(x: torch.Tensor, ldx: int, hx: int, w: torch.Tensor, out: torch.Tensor, ldo: int, ho: int,
+                  m: int, alpha: float = 1.0) -> None:
+    """out[t, h, :] = alpha * w[h] @ x[t, h, :] for w [H, N, K]; x[t, h] starts at t * ldx + h * hx elements
+    into x, out[t, h] at t * ldo + h * ho into out."""
+    H, N, K = w.shape
+    if not w.is_contiguous():
+        raise KernelError("headwise_gemm: the weights must be contiguous [H, N, K]")
+    kernel("latent_attention", "gg_headwise_gemm")(_p(x), dtype_code(x.dtype), int(ldx), int(hx), _p(w),
+                                                    dtype_code(w.dtype), _p(out), dtype_code(out.dtype), int(ldo),
+                                                    int(ho), int(m), N, K, H, float(alpha), _stream())
+
+
+def latent_attention_plain(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                           seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int, n_tokens: int,
+                           heads: int, R: int, r: int, scale: float, window: int) -> None:
+    from .tcgen05_gemm import status_word
+    kernel("latent_attention", "gg_latent_attention_plain")(
+        _p(qcat), dtype_code(qcat.dtype), _p(pool), dtype_code(pool.dtype), pool.shape[-1], _p(out),
+        dtype_code(out.dtype), _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], int(page_size),
+        pool.shape[0], n_tokens, heads, R, r, float(scale), int(window), _p(status_word(qcat.device)), _stream())
+
+
+# ------------------------------------------------------------------------------- routed experts
+def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, seq_of_token: Optional[torch.Tensor],
+              softmax: bool = False, renormalize: bool = False, rows: Optional[int] = None) -> None:
+    _need(z, torch.float32, "router logits")
+    _need(idx, torch.int32, "idx")
+    _need(wts, torch.float32, "wts")
+    T = z.shape[0] if rows is None else rows
+    kernel("moe", "gg_moe_route")(_p(z), T, z.shape[-1], int(top), int(softmax), int(renormalize), _p(idx), _p(wts),
+                                   _p(seq_of_token), _stream())
+
+
+def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
+                n_tokens: int, top: int, weight_on_input: bool, limit: float, slope: float, out_scale: float) -> None:
+    """y[t * top + k] = out_scale * act(Wg[e] x, Wu[e] x) for e = idx[t, k]; w_gu [E, 2, F, W]."""
+    E, two, F, W = w_gu.shape
+    if two != 2 or h.shape[-1] != W or not h.is_contiguous() or not w_gu.is_contiguous() or not y.is_contiguous():
+        raise KernelError("moe_gate_up: shapes disagree")
+    kernel("moe", "gg_moe_gate_up")(_p(h), dtype_code(h.dtype), _p(w_gu), dtype_code(w_gu.dtype), _p(idx), _p(wts),
+                                     _p(y), dtype_code(y.dtype), n_tokens, W, F, int(top), int(weight_on_input),
+                                     float(limit), float(slope), float(out_scale), _stream())
+
+
+def moe_down(y: torch.Tensor, w_d: torch.Tensor, idx: torch.Tensor, residual: torch.Tensor, n_tokens: int, top: int,
+             seq_of_token: Optional[torch.Tensor]) -> None:
+    """residual[t] += sum_k Wd[idx[t, k]] y[t * top + k]; w_d [E, W, F]."""
+    E, W, F = w_d.shape
+    _need(residual, torch.float32, "residual")
+    if residual.shape[-1] != W or not w_d.is_contiguous() or not y.is_contiguous():
+        raise KernelError("moe_down: shapes disagree")
+    kernel("moe", "gg_moe_down")(_p(y), dtype_code(y.dtype), _p(w_d), dtype_code(w_d.dtype), _p(idx), _p(residual),
+                                  n_tokens, W, F, int(top), _p(seq_of_token), _stream())
 
 
 def wait_probe(limit_cycles: int, code: int, status: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,177 @@
+// Routed experts: the router's choice, and the experts' products through an index (no sorting, no host
+// round trip), for steps of few tokens and for the 32-bit path.
+//
+//   route:    s = score(z) per expert (sigmoid, or softmax over all experts); the `top` largest are chosen
+//             (ties go to the lower index); weights are the chosen scores, optionally divided by their sum.
+//   gate_up:  for pair p = (token t, choice k) with expert e: x = h[t] (times the weight if the weight sits on
+//             the expert's input); g = Wg[e] x, u = Wu[e] x; y[p] = out_scale * act(g, u) (times the weight if
+//             it sits on the output).
+//   down:     residual[t] += sum_k Wd[e(t, k)] y[t, k]  (k in order: the sum does not depend on the batch).
+//
+// act "clamped glu": g' = min(g, L), u' = clamp(u, -L, L), g' * sigmoid(slope g') * (u' + 1).
+// Router scores, the choice, the weights and all sums are float32.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- route
+// One warp per token.  z [T, E] float32 logits.  softmax != 0: scores are softmax(z), else sigmoid(z).
+__global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, int top, int softmax, int renorm,
+                                                       int* idx, float* wts, const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* zt = z + (size_t)t * E;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) {      // padding: expert 0 with weight 0
+        for (int k = lane; k < top; k += 32) { idx[(size_t)t * top + k] = 0; wts[(size_t)t * top + k] = 0.f; }
+        return;
+    }
+    float mx = -INFINITY, den = 1.f;
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zt[e]);
+        mx = warp_max(mx);
+        float s = 0.f;
+        for (int e = lane; e < E; e += 32) s += expf(zt[e] - mx);
+        den = warp_sum(s);
+    }
+    float total = 0.f;
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int k = 0; k < top; ++k) {
+        // the largest logit after (prev_v, prev_i) in the order (value descending, index ascending)
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = zt[e];
+            const bool after = v < prev_v || (v == prev_v && e > prev_i);
+            if (after && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        const float s = softmax ? expf(bv - mx) / den : 1.0f / (1.0f + expf(-bv));
+        if (lane == 0) { idx[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = s; }
+        total += s;
+        prev_v = bv;
+        prev_i = bi;
+    }
+    if (renorm) {
+        __syncwarp();
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] /= total;
+    }
+}
+
+GG_API gg_moe_route(const float* z, int T, int E, int top, int softmax, int renorm, int* idx, float* wts,
+                    const int* seq_of_token, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E) return GG_ERR_ARG;
+    gg_launch(moe_route_kernel, dim3(T), dim3(32), 0, stream, 1, z, E, top, softmax, renorm, idx, wts, seq_of_token);
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- activation
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
+
+// ----------------------------------------------------------------------------- gate and up through the index
+// grid (pairs, ceil(F / 8)); 8 warps, one feature each: the two rows Wg[e][f], Wu[e][f] against x in shared memory.
+// w_gu [E][2][F][W]: an expert's gate rows, then its up rows.
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(const TX* h, const TW* __restrict__ w_gu, const int* idx,
+                                                          const float* wts, TY* y, int W, int F, int top,
+                                                          int weight_on_input, float limit, float slope, float out_scale) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float xs[];
+    const int p = blockIdx.x, t = p / top;
+    const int e = idx[p];
+    const float wt = wts[p];
+    const float xin = weight_on_input ? wt : 1.0f;
+    const TX* ht = h + (size_t)t * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = to_f<TX>(ht[i]) * xin;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f = blockIdx.y * 8 + warp;
+    if (f >= F) return;
+    const TW* wg = w_gu + ((size_t)e * 2 * F + f) * W;
+    const TW* wu = wg + (size_t)F * W;
+    float g = 0.f, u = 0.f;
+    for (int i = lane; i < W; i += 32) {
+        const float x = xs[i];
+        g = fmaf(to_f<TW>(wg[i]), x, g);
+        u = fmaf(to_f<TW>(wu[i]), x, u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+        float a = clamped_glu(g, u, limit, slope) * out_scale;
+        if (!weight_on_input) a *= wt;
+        y[(size_t)p * F + f] = from_f<TY>(a);
+    }
+}
+
+GG_API gg_moe_gate_up(const void* h, int h_dtype, const void* w_gu, int w_dtype, const int* idx, const float* wts,
+                      void* y, int y_dtype, int T, int W, int F, int top, int weight_on_input, float limit,
+                      float slope, float out_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 48 * 1024 || (F + 7) / 8 > 65535) return GG_ERR_ARG;
+    dim3 grid(T * top, (F + 7) / 8);
+    const size_t smem = (size_t)W * sizeof(float);
+#define GG_GU(TX, TW, TY) gg_launch(moe_gate_up_kernel<TX, TW, TY>, dim3(grid), dim3(256), smem, stream, 1, (const TX*)h, \
+        (const TW*)w_gu, idx, wts, (TY*)y, W, F, top, weight_on_input, limit, slope, out_scale)
+    if (h_dtype == GG_F32 && w_dtype == GG_F32 && y_dtype == GG_F32) GG_GU(float, float, float);
+    else if (h_dtype == GG_BF16 && w_dtype == GG_BF16 && y_dtype == GG_F32) GG_GU(bf16, bf16, float);
+    else if (h_dtype == GG_BF16 && w_dtype == GG_BF16 && y_dtype == GG_BF16) GG_GU(bf16, bf16, bf16);
+    else return GG_ERR_DTYPE;
+#undef GG_GU
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- down through the index
+// grid (tokens, ceil(W / 8)); one warp per output element of the token; y[t, k] in shared memory.
+// w_d [E][W][F].
+template <typename TY, typename TW>
+__global__ void __launch_bounds__(256) moe_down_kernel(const TY* y, const TW* __restrict__ w_d, const int* idx,
+                                                       float* residual, int W, int F, int top,
+                                                       const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float ys[];
+    const int t = blockIdx.x;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
+    const TY* yt = y + (size_t)t * top * F;
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x) ys[i] = to_f<TY>(yt[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.y * 8 + warp;
+    if (n >= W) return;
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = idx[(size_t)t * top + k];
+        const TW* wr = w_d + ((size_t)e * W + n) * F;
+        float s = 0.f;
+        for (int i = lane; i < F; i += 32) s = fmaf(to_f<TW>(wr[i]), ys[k * F + i], s);
+        total += warp_sum(s);
+    }
+    if (lane == 0) residual[(size_t)t * W + n] += total;
+}
+
+GG_API gg_moe_down(const void* y, int y_dtype, const void* w_d, int w_dtype, const int* idx, float* residual, int T,
+                   int W, int F, int top, const int* seq_of_token, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (W <= 0 || F <= 0 || top <= 0 || (size_t)top * F * 4 > 48 * 1024 || (W + 7) / 8 > 65535) return GG_ERR_ARG;
+    dim3 grid(T, (W + 7) / 8);
+    const size_t smem = (size_t)top * F * sizeof(float);
+#define GG_DN(TY, TW) gg_launch(moe_down_kernel<TY, TW>, dim3(grid), dim3(256), smem, stream, 1, (const TY*)y, \
+        (const TW*)w_d, idx, residual, W, F, top, seq_of_token)
+    if (y_dtype == GG_F32 && w_dtype == GG_F32) GG_DN(float, float);
+    else if (y_dtype == GG_F32 && w_dtype == GG_BF16) GG_DN(float, bf16);
+    else if (y_dtype == GG_BF16 && w_dtype == GG_BF16) GG_DN(bf16, bf16);
+    else return GG_ERR_DTYPE;
+#undef GG_DN
+    return gg_last_error();
+}

@@ -6,6 +6,7 @@ from typing import Dict
 import torch
 
 from ..config.spec import BlockSpec
+from ..csrc import kernels as K
 from .base import RowStats, Runtime, StepContext
 from .registry import register_arrangement
 
@@ -52,6 +53,48 @@ class PreNormBlock:
         if stats is not None:
             stats.fresh = False        # the part is about to change the residual rows
         return h
+
+
+@register_arrangement("parallel")
+class ParallelBlock:
+    """h = norm(x); x += mult * (mixer(h) + feed_forward(h)): one norm whose output both parts read, and a
+    factor `residual_mult` (a parameter of the block spec, default 1) on what the block adds.  The
+    feed-forward may be absent.  A part that has ``scale_output(mult) -> bool`` and accepts takes the factor
+    into its own last product and adds straight into the residual stream; any other part is handed a zeroed
+    float32 buffer and the block adds `mult` times that buffer itself."""
+
+    roles = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional_roles = ("feed_forward",)
+
+    def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
+        self.parts = dict(parts)
+        self.rt = rt
+        self.norm, self.mixer = parts["norm"], parts["mixer"]
+        self.feed_forward = parts.get("feed_forward")
+        self.mult = float(spec.params.get("residual_mult", 1.0))
+        self._direct = {}
+        for role in ("mixer", "feed_forward"):
+            part = parts.get(role)
+            if part is None:
+                continue
+            take = getattr(part, "scale_output", None)
+            self._direct[role] = self.mult == 1.0 or (take is not None and bool(take(self.mult)))
+
+    def _run(self, role: str, x: torch.Tensor, ctx: StepContext, call) -> None:
+        if self._direct[role]:
+            call(x)
+            return
+        buf = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
+        buf.zero_()
+        call(buf)
+        K.residual_axpy(x, buf, self.mult)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache, writes_cache: bool) -> None:
+        h = ctx.ws.get("block_normed", tuple(x.shape), self.rt.dtype)
+        self.norm.forward(x, h)
+        self._run("mixer", x, ctx, lambda dst: self.mixer.forward(h, dst, ctx, cache, writes_cache))
+        if self.feed_forward is not None:
+            self._run("feed_forward", x, ctx, lambda dst: self.feed_forward.forward(h, dst, ctx))
 
 
 def _offer_norm(part, norm, rt: Runtime) -> bool:

@@ -15,15 +15,15 @@ from .registry import register_embedding, register_head
 @register_embedding("embedding")
 class TokenEmbedding:
     """x = E[token]: a row gather into the float32 residual stream, no scaling
-    (pkg/model/qwen3/model.go:169-196)."""
+    (pkg/model/qwen3/model.go:169-196).  ``tensor`` of the spec names the stored table (default "weight")."""
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl(shape=(spec["vocab_size"], spec["hidden_size"]))}
+        return {spec.get("tensor", "weight"): TensorDecl(shape=(spec["vocab_size"], spec["hidden_size"]))}
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
-        self.weight = rt.matrix(weights["weight"])
+        self.weight = rt.matrix(weights[spec.get("tensor", "weight")])
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
         K.embed_gather(self.weight, tokens, out)

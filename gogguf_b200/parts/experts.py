@@ -1,0 +1,152 @@
+"""Feed-forwards beyond the dense SwiGLU: a two-matrix layer around the xIELU activation, and routed experts.
+
+xIELU (`xielu_mlp`): down(f(up h)) with f(z) = a_p z^2 + z/2 for z > 0 and a_q (exp(z) - 1 - z) + z/2 otherwise,
+a_p = softplus(p), a_q = 1/2 + softplus(q); the stored tensor `act` holds (p, q).
+
+Routed experts (`routed_experts`): router logits W_r h in float32, scores by sigmoid (or softmax), the `top_k`
+largest chosen, weights the chosen scores (optionally renormalised), the weight applied to the expert's input
+or to its output.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
+act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
+Steps of few tokens (and the 32-bit path) reach the experts' matrices through the chosen index, token by
+token, with nothing read back; steps of many tokens in bfloat16 sort the (token, choice) pairs by expert and run
+one tensor-core product per expert on its rows.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import kernels as K
+from ..weights.loader import TensorDecl
+from .base import Linear, Runtime, StepContext
+from .registry import register_feed_forward
+
+
+def _softplus(v: float) -> float:
+    return math.log1p(math.exp(-abs(v))) + max(v, 0.0)
+
+
+@register_feed_forward("xielu_mlp")
+class XieluMLP:
+    @classmethod
+    def _names(cls, spec: PartSpec) -> Dict[str, str]:
+        n = dict(up="up_proj.weight", down="down_proj.weight", act="act")
+        n.update(spec.get("names") or {})
+        return n
+
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
+        h, i = spec["hidden_size"], spec["intermediate_size"]
+        n = cls._names(spec)
+        return {n["up"]: TensorDecl(shape=(i, h)), n["down"]: TensorDecl(shape=(h, i)),
+                n["act"]: TensorDecl(shape=(2,), init="small_normal")}
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.rt = rt
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        n = self._names(spec)
+        self.up = Linear(weights[n["up"]], rt)
+        self.down = Linear(weights[n["down"]], rt)
+        p, q = (float(v) for v in weights[n["act"]].detach().float().cpu().tolist())
+        self.ap, self.aq = _softplus(p), 0.5 + _softplus(q)
+        self.out_scale = 1.0
+
+    def scale_output(self, mult: float) -> bool:
+        """The factor goes onto the activation in float32, before it is rounded for the down projection."""
+        self.out_scale = float(mult)
+        return True
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        T = ctx.n_tokens
+        z = ctx.ws.get("ffn_act", (T, self.inter), self.rt.dtype)
+        self.up(h, z, ws=ctx.ws)
+        K.xielu(z, z, self.ap, self.aq, self.out_scale)
+        self.down(z, residual, accumulate=True, ws=ctx.ws)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts:
+    @classmethod
+    def _names(cls, spec: PartSpec) -> Dict[str, str]:
+        n = dict(router="router.weight", expert="experts.{}.", gate="gate_proj.weight", up="up_proj.weight",
+                 down="down_proj.weight")
+        n.update(spec.get("names") or {})
+        return n
+
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
+        h, i, E = spec["hidden_size"], spec["intermediate_size"], spec["num_experts"]
+        n = cls._names(spec)
+        t = {n["router"]: TensorDecl(shape=(E, h))}
+        for e in range(E):
+            p = n["expert"].format(e)
+            t[p + n["gate"]] = TensorDecl(shape=(i, h))
+            t[p + n["up"]] = TensorDecl(shape=(i, h))
+            t[p + n["down"]] = TensorDecl(shape=(h, i))
+        return t
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.rt = rt
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.E, self.top = int(spec["num_experts"]), int(spec["top_k"])
+        score = spec.get("score", "sigmoid")
+        if score not in ("sigmoid", "softmax"):
+            raise ValueError(f"routed experts: unknown score {score!r} (sigmoid, softmax)")
+        self.softmax = score == "softmax"
+        self.renorm = bool(spec.get("renormalize", False))
+        where = spec.get("weight_on", "output")
+        if where not in ("input", "output"):
+            raise ValueError(f"routed experts: weight_on must be 'input' or 'output', got {where!r}")
+        self.on_input = where == "input"
+        act = dict(spec.get("activation") or {})
+        if act.get("kind", "clamped_glu") != "clamped_glu":
+            raise ValueError(f"routed experts: unknown activation {act.get('kind')!r} (clamped_glu)")
+        self.limit = float(act.get("limit", float("inf")))
+        self.slope = float(act.get("slope", 1.0))
+        n = self._names(spec)
+        self.router_w = rt.matrix(weights[n["router"]])
+        gu: List[torch.Tensor] = []
+        dn: List[torch.Tensor] = []
+        for e in range(self.E):
+            p = n["expert"].format(e)
+            g, u = rt.matrix(weights.pop(p + n["gate"])), rt.matrix(weights.pop(p + n["up"]))
+            if g.dtype != u.dtype:
+                g, u = g.float(), u.float()
+            gu.append(torch.stack([g, u], dim=0))
+            dn.append(rt.matrix(weights.pop(p + n["down"])))
+        if len({t.dtype for t in gu} | {t.dtype for t in dn}) != 1:
+            gu, dn = [t.float() for t in gu], [t.float() for t in dn]
+        self.w_gu = torch.stack(gu, dim=0).contiguous()       # [E, 2, F, W]
+        self.w_d = torch.stack(dn, dim=0).contiguous()        # [E, W, F]
+        self.out_scale = 1.0
+        self._grouped = None
+        if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16:
+            from . import experts_grouped
+            self._grouped = experts_grouped.try_make(self)
+
+    def scale_output(self, mult: float) -> bool:
+        """The factor goes onto the experts' activations in float32 (the down projections are linear)."""
+        self.out_scale = float(mult)
+        return True
+
+    def route(self, h: torch.Tensor, ctx: StepContext):
+        T = ctx.n_tokens
+        z = ctx.ws.get("moe_logits", (T, self.E), torch.float32)
+        K.gemm_plain(h, self.router_w, z, m=T)           # CUDA cores, float32 sums: the router is never reduced
+        idx = ctx.ws.get("moe_idx", (T, self.top), torch.int32)
+        wts = ctx.ws.get("moe_wts", (T, self.top), torch.float32)
+        K.moe_route(z, self.top, idx, wts, ctx.seq_of_token, softmax=self.softmax, renormalize=self.renorm, rows=T)
+        return idx, wts
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        T = ctx.n_tokens
+        idx, wts = self.route(h, ctx)
+        if self._grouped is not None and self._grouped.takes(T):
+            self._grouped.run(h, idx, wts, residual, ctx)
+            return
+        y = ctx.ws.get("moe_act", (T * self.top, self.inter), torch.float32)
+        K.moe_gate_up(h, self.w_gu, idx, wts, y, T, self.top, self.on_input, self.limit, self.slope, self.out_scale)
+        K.moe_down(y, self.w_d, idx, residual, T, self.top, ctx.seq_of_token)

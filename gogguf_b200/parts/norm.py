@@ -1,4 +1,8 @@
-"""RMSNorm: out = x * (1/sqrt(mean(x^2) + eps)) * weight (pkg/ops/rmsnorm.go:10-25)."""
+"""RMSNorm: out = x * (1/sqrt(mean(x^2) + eps)) * weight (pkg/ops/rmsnorm.go:10-25).
+
+Two optional parameters of the spec: ``tensor`` names the stored vector under the part's prefix (default
+"weight"), and ``weight_offset`` is added to the stored vector when the model is built, for checkpoints that
+keep their norm weights as the distance from one (the factor applied is then 1 + w)."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -20,12 +24,17 @@ class RMSNorm:
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl(shape=(spec["size"],), init="ones_normal")}
+        offset = float(spec.get("weight_offset", 0.0))
+        return {spec.get("tensor", "weight"): TensorDecl(shape=(spec["size"],),
+                                                         init="ones_normal" if offset == 0.0 else "zeros_normal")}
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
-        self.weight = rt.vector(weights["weight"])
+        self.weight = rt.vector(weights[spec.get("tensor", "weight")])
+        offset = float(spec.get("weight_offset", 0.0))
+        if offset != 0.0:
+            self.weight = (self.weight + offset).contiguous()      # float32: the sum is exact to a rounding
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         """x: float32 rows of the residual stream; out: compute dtype; rows: optional row gather."""

@@ -16,6 +16,8 @@ class RotaryNeoX:
     (pkg/ops/rope_tables.go:6-20, pkg/ops/rope_heads.go:30-38).  Angles, cos and sin are computed in
     float64 once per step for all layers that share (theta, rotary_dim) and stored as float32."""
 
+    pairing = "halves"
+
     def __init__(self, params: Dict[str, Any], rt: Runtime):
         self.theta = float(params["theta"])
         self.rotary_dim = int(params["rotary_dim"])
@@ -25,7 +27,7 @@ class RotaryNeoX:
         i = torch.arange(half, dtype=torch.float64)
         self.inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64),
                                   -2.0 * i / self.rotary_dim).to(rt.device)
-        self.key = ("rope_neox", self.theta, self.rotary_dim)
+        self.key = ("rope", self.theta, self.rotary_dim)     # the tables do not depend on the pairing
 
     def tables(self, ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor]:
         got = ctx.shared.get(self.key)
@@ -36,3 +38,13 @@ class RotaryNeoX:
             K.rope_tables(ctx.positions, self.inv_freq, cos, sin)
             got = ctx.shared[self.key] = (cos, sin)
         return got
+
+
+@register_position("rope_adjacent")
+class RotaryAdjacent(RotaryNeoX):
+    """The same angles with the other pairing: element 2i turns with element 2i + 1 (the interleaved layout),
+    angle = pos * theta^(-2i/rotary_dim).  The tables are those of `RotaryNeoX` (column i is pair i), so layers
+    of both kinds with equal base and size share them; which elements form a pair is the business of the
+    kernel that applies them, and a mixer states the pairing it implements in `pairing`."""
+
+    pairing = "adjacent"

@@ -40,7 +40,8 @@ class WeightsError(ValueError):
 class TensorDecl:
     """What a part expects of one tensor.
 
-    init: "normal" (N(0, std)), "ones_normal" (1 + N(0, norm_std)) or "zeros";
+    init: "normal" (N(0, std)), "ones_normal" (1 + N(0, norm_std)), "zeros_normal" (N(0, norm_std)),
+    "small_normal" (N(0, 0.5)) or "zeros";
     used only by the random-weights mode.  optional: may be absent (for
     instance a separate head matrix of a model with tied embeddings).
     """
@@ -157,6 +158,10 @@ def random_tensors(expected: Mapping[str, TensorDecl], seed: int, std: float, no
                 t.mul_(std)
             elif d.init == "ones_normal":
                 t.mul_(norm_std).add_(1.0)
+            elif d.init == "zeros_normal":       # a norm weight stored as its distance from one
+                t.mul_(norm_std)
+            elif d.init == "small_normal":       # scalars of an activation, around zero
+                t.mul_(0.5)
             else:
                 raise ValueError(f"tensor {name!r}: unknown init {d.init!r}")
         out[name] = t.to(dtype)
