@@ -1,6 +1,69 @@
-"""Host side of the tensor-core latent attention kernels (csrc/latent_attention.cu)."""
+"""Host side of the tensor-core latent attention kernels (csrc/latent_attention.cu): the per-head products
+and the attention over the latent cache on mma.sync, for bfloat16."""
 from __future__ import annotations
 
+from typing import Optional
 
-def try_make(heads: int, latent_dim: int, rope_dim: int, scale: float, window: int):
-    return None
+import torch
+
+from .build import KernelError, kernel, module
+
+
+def headwise_gemm_mma(x: torch.Tensor, ldx: int, hx: int, w: torch.Tensor, out: torch.Tensor, ldo: int, ho: int,
+                      m: int, alpha: float = 1.0) -> None:
+    """out[t, h, :] = alpha * w[h] @ x[t, h, :] on the tensor cores; bfloat16 x and w [H, N, K], K, ldx and hx
+    multiples of 8, out bfloat16 or float32."""
+    H, N, K = w.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous():
+        raise KernelError("headwise_gemm_mma takes bfloat16 operands, the weights contiguous [H, N, K]")
+    from .kernels import dtype_code
+    kernel("latent_attention", "gg_headwise_gemm_mma")(
+        x.data_ptr(), int(ldx), int(hx), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), int(ldo), int(ho),
+        int(m), N, K, H, float(alpha), torch.cuda.current_stream().cuda_stream)
+
+
+def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
+                         positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
+                         page_size: int, n_seqs: int, n_tokens: int, heads: int, R: int, r: int, scale: float,
+                         window: int) -> None:
+    for t in (qcat, pool, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("latent_attention_mma takes bfloat16 queries, cache and output")
+    from .tcgen05_gemm import status_word
+    kernel("latent_attention", "gg_latent_attention_mma")(
+        qcat.data_ptr(), pool.data_ptr(), pool.shape[-1], out.data_ptr(), cu_seqlens.data_ptr(), positions.data_ptr(),
+        seq_of_token.data_ptr(), page_table.data_ptr(), page_table.shape[-1], int(page_size), pool.shape[0],
+        int(n_seqs), int(n_tokens), heads, R, r, float(scale), int(window), status_word(qcat.device).data_ptr(),
+        torch.cuda.current_stream().cuda_stream)
+
+
+def mma_takes(R: int, r: int) -> bool:
+    return bool(module("latent_attention").lib.gg_latent_attention_mma_takes(int(R), int(r)))
+
+
+class _Fast:
+    def __init__(self, heads: int, R: int, r: int, scale: float, window: int):
+        self.H, self.R, self.r, self.scale, self.window = heads, R, r, scale, window
+
+    def absorb(self, qd: torch.Tensor, ldx: int, hx: int, uk_t: torch.Tensor, qcat: torch.Tensor, m: int) -> None:
+        """qcat[t, h, :R] = Wuk_h^T q_plain[t, h]."""
+        D = self.R + self.r
+        headwise_gemm_mma(qd, ldx, hx, uk_t, qcat, self.H * D, D, m)
+
+    def attention(self, qcat, pool, out, ctx, table, page_size: int) -> None:
+        latent_attention_mma(qcat, pool, out, ctx.cu_seqlens, ctx.positions, ctx.seq_of_token, table, page_size,
+                             ctx.n_seqs, ctx.n_tokens, self.H, self.R, self.r, self.scale, self.window)
+
+    def expand(self, olat: torch.Tensor, uv: torch.Tensor, av: torch.Tensor, m: int, alpha: float) -> None:
+        """av[t, h, :] = alpha * Wuv_h olat[t, h]."""
+        dv = uv.shape[1]
+        headwise_gemm_mma(olat, self.H * self.R, self.R, uv, av, self.H * dv, dv, m, alpha)
+
+
+def try_make(heads: int, nope_dim: int, latent_dim: int, rope_dim: int, row_stride: int, scale: float,
+             window: int) -> Optional[_Fast]:
+    """The tensor-core forms for bfloat16, or None when the sizes are outside what they take (latent and rotated
+    sizes multiples of 16, every row of the q / down product on a 16-byte boundary); the plain kernels then serve."""
+    if nope_dim % 8 or (nope_dim + rope_dim) % 8 or row_stride % 8 or not mma_takes(latent_dim, rope_dim):
+        return None
+    return _Fast(heads, latent_dim, rope_dim, scale, window)

@@ -288,4 +288,349 @@ GG_API gg_latent_attention_plain(const void* qcat, int q_dtype, const void* pool
     return gg_last_error();
 }
 
+// ----------------------------------------------------------------------------- tensor-core helpers (mma.sync)
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void zero16(void* smem) { *reinterpret_cast<uint4*>(smem) = make_uint4(0u, 0u, 0u, 0u); }
+
+// ----------------------------------------------------------------------------- per-head products on mma.sync
+// The same contract as headwise_gemm_kernel for bfloat16 operands whose rows start on 16-byte boundaries
+// (K, ldx and hx multiples of 8).  A CTA computes 64 tokens x 64 outputs of one head; x and w rows are staged
+// 64 columns of k at a time (rows padded by 8 elements, so ldmatrix reads without bank conflicts).
+#define HM_KS 64
+#define HM_LD (HM_KS + 8)
+template <typename TO>
+__global__ void __launch_bounds__(128) headwise_mma_kernel(const bf16* x, long long ldx, long long hx,
+                                                           const bf16* __restrict__ w, TO* out, long long ldo,
+                                                           long long ho, int M, int N, int K, float alpha) {
+    pdl_launch();
+    __shared__ __align__(16) bf16 xs[64 * HM_LD];
+    __shared__ __align__(16) bf16 ws[64 * HM_LD];
+    const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bf16* xh = x + (size_t)h * hx;
+    const bf16* wh = w + (size_t)h * N * K;
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    pdl_wait();
+    for (int k0 = 0; k0 < K; k0 += HM_KS) {
+        for (int c = tid; c < 64 * (HM_KS / 8); c += 128) {
+            const int row = c / (HM_KS / 8), kc = (c % (HM_KS / 8)) * 8;
+            bf16* dx = xs + row * HM_LD + kc;
+            bf16* dw = ws + row * HM_LD + kc;
+            if (m0 + row < M && k0 + kc < K) cp_async16(dx, xh + (size_t)(m0 + row) * ldx + k0 + kc); else zero16(dx);
+            if (n0 + row < N && k0 + kc < K) cp_async16(dw, wh + (size_t)(n0 + row) * K + k0 + kc); else zero16(dw);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < HM_KS / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(a, xs + (warp * 16 + (lane & 15)) * HM_LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                ldsm_x4(b, ws + (np * 16 + (lane & 7) + (lane >> 4) * 8) * HM_LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(acc[2 * np], a, b[0], b[1]);
+                mma16816(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, q4 = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        const int n = n0 + nt * 8 + 2 * q4;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = m0 + warp * 16 + g + half * 8;
+            if (m >= M) continue;
+            TO* o = out + (size_t)m * ldo + (size_t)h * ho + n;
+            if (n < N) o[0] = from_f<TO>(acc[nt][2 * half] * alpha);
+            if (n + 1 < N) o[1] = from_f<TO>(acc[nt][2 * half + 1] * alpha);
+        }
+    }
+}
+
+GG_API gg_headwise_gemm_mma(const void* x, long long ldx, long long hx, const void* w, void* out, int out_dtype,
+                            long long ldo, long long ho, int M, int N, int K, int H, float alpha, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || H <= 0) return 0;
+    if (K <= 0 || (K % 8) || (ldx % 8) || (hx % 8) || (((uintptr_t)x) & 15) || (((uintptr_t)w) & 15) || H > 65535 ||
+        (M + 63) / 64 > 65535)
+        return GG_ERR_ARG;
+    dim3 grid((N + 63) / 64, (M + 63) / 64, H);
+    GG_DISPATCH_DTYPE(out_dtype, TO,
+        gg_launch(headwise_mma_kernel<TO>, dim3(grid), dim3(128), 0, stream, 1, (const bf16*)x, ldx, hx,
+                  (const bf16*)w, (TO*)out, ldo, ho, M, N, K, alpha));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- attention on mma.sync
+// A CTA of four warps takes 64 consecutive rows of one sequence's new (token, head) pairs, head fastest, so its
+// rows belong to a few consecutive tokens and share one range of cached positions: from the first token's
+// window start to the last token's own position.  That range is streamed in tiles of KT positions (cp.async, two
+// stages); per tile S = Q K^T over all R + r columns (Q in shared memory, fragments by ldmatrix), the causal and
+// window mask per row, an online softmax in float32, and O += P V where V is the first R columns of the very
+// tile K was read from.  A CTA keeps RC columns of O in registers; a latent wider than RC is covered by
+// gridDim.y CTAs that repeat the scores and own RC columns each.  Rows past the sequence's pairs are not written.
+template <int KT, int RC>
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+    const bf16* qcat, const bf16* pool, int pool_row, bf16* out, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
+    int max_pages, int page_size, int n_seqs, int H, int R, int r, float scale_log2, int window, const PageBounds pb) {
+    pdl_launch();
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int D = R + r, LD = D + 8;
+    bf16* qs = reinterpret_cast<bf16*>(smraw);          // [64][LD]
+    bf16* ks = qs + 64 * LD;                            // [2][KT][LD]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // which sequence and which 64 rows of it
+    int b = 0, chunk = blockIdx.x, t0 = 0, n_new = 0;
+    for (; b < n_seqs; ++b) {
+        t0 = cu_seqlens[b];
+        n_new = cu_seqlens[b + 1] - t0;
+        const int chunks = (n_new * H + 63) / 64;
+        if (chunk < chunks) break;
+        chunk -= chunks;
+    }
+    if (b >= n_seqs) return;
+    const int rows_total = n_new * H;
+    const int f0 = chunk * 64;
+    const int rows_here = min(64, rows_total - f0);
+    const int z0 = blockIdx.y * RC;                      // first latent column of this CTA's share of O
+    bf16* orow0 = out + ((size_t)t0 * H + f0) * R;
+    pdl_wait();                                          // nothing is written, and no activation read, before this
+    if (seq_of_token[t0] < 0) {                          // a padding sequence: zero rows
+        for (int i = tid; i < rows_here * RC; i += 128) {
+            const int c = z0 + i % RC;
+            if (c < R) orow0[(size_t)(i / RC) * R + c] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
+    const int tl0 = f0 / H, tl1 = (f0 + rows_here - 1) / H;
+    const int pos0 = positions[t0 + tl0], pos1 = pos0 + (tl1 - tl0);
+    int key_lo = 0;
+    if (window > 0 && pos0 - window + 1 > 0) key_lo = pos0 - window + 1;
+    const int tile0 = key_lo / KT, ntiles = pos1 / KT - tile0 + 1;
+    const int* pt = page_table + (size_t)b * max_pages;
+    const int chunks_per_row = D / 8;
+
+    auto load_keys = [&](int tile, int stage) {
+        bf16* dst = ks + (size_t)stage * KT * LD;
+        const int j0 = tile * KT;
+        for (int c = tid; c < KT * chunks_per_row; c += 128) {
+            const int kk = c / chunks_per_row, col = (c % chunks_per_row) * 8;
+            const int j = j0 + kk;
+            bf16* d = dst + kk * LD + col;
+            if (j <= pos1) {
+                const int page = gg_page(pt, j / page_size, max_pages, pb, 51);
+                cp_async16(d, pool + ((size_t)page * page_size + (j % page_size)) * pool_row + col);
+            } else {
+                zero16(d);
+            }
+        }
+    };
+    {   // the queries of this CTA: rows_here consecutive rows of qcat
+        const bf16* qsrc = qcat + ((size_t)t0 * H + f0) * D;
+        for (int c = tid; c < 64 * chunks_per_row; c += 128) {
+            const int row = c / chunks_per_row, col = (c % chunks_per_row) * 8;
+            bf16* d = qs + row * LD + col;
+            if (row < rows_here) cp_async16(d, qsrc + (size_t)row * D + col); else zero16(d);
+        }
+    }
+    load_keys(tile0, 0);
+    cp_async_commit();
+
+    const int g = lane >> 2, q4 = lane & 3;
+    int prow[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int f = f0 + warp * 16 + g + 8 * i;
+        valid[i] = f < rows_total;
+        prow[i] = pos0 + (f / H - tl0);
+    }
+    float o[RC / 8][4];
+#pragma unroll
+    for (int i = 0; i < RC / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    const int ksteps = D / 16;
+    const int ocols = min(RC, R - z0);                   // columns of O this CTA owns (a multiple of 16)
+
+    for (int it = 0; it < ntiles; ++it) {
+        if (it + 1 < ntiles) {
+            load_keys(tile0 + it + 1, (it + 1) & 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* kt = ks + (size_t)(it & 1) * KT * LD;
+        float s[KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < KT / 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+        for (int kk = 0; kk < ksteps; ++kk) {
+            uint32_t a[4];
+            ldsm_x4(a, qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < KT / 16; ++np) {
+                uint32_t bb[4];
+                ldsm_x4(bb, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(s[2 * np], a, bb[0], bb[1]);
+                mma16816(s[2 * np + 1], a, bb[2], bb[3]);
+            }
+        }
+        // mask, running maximum and sum (two rows per thread; a row's 4 threads hold its KT scores)
+        const int j0 = (tile0 + it) * KT;
+        float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int j = j0 + nt * 8 + 2 * q4 + (e & 1);
+                const bool see = valid[i] && j <= prow[i] && (window <= 0 || j > prow[i] - window);
+                const float v = see ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mnew[i] = fmaxf(mnew[i], v);
+            }
+        float corr[2], muse[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
+            mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
+            muse[i] = mnew[i] == -INFINITY ? 0.f : mnew[i];
+            corr[i] = exp2f(mrow[i] - muse[i]);          // 0 while the row has seen nothing
+            mrow[i] = mnew[i];
+            lrow[i] *= corr[i];
+        }
+        uint32_t pfrag[KT / 16][4];
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) {
+            const float p0 = exp2f(s[nt][0] - muse[0]), p1 = exp2f(s[nt][1] - muse[0]);
+            const float p2 = exp2f(s[nt][2] - muse[1]), p3 = exp2f(s[nt][3] - muse[1]);
+            lrow[0] += p0 + p1;
+            lrow[1] += p2 + p3;
+            // the C fragments of two neighbouring 8-key tiles are the A fragment of one 16-key step
+            pfrag[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+            pfrag[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int i = 0; i < RC / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V, V[key][col] = tile[key][z0 + col]
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+#pragma unroll
+            for (int np = 0; np < RC / 16; ++np) {
+                if (np * 16 < ocols) {
+                    uint32_t bb[4];
+                    ldsm_x4_trans(bb, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + z0 + np * 16 + (lane >> 4) * 8);
+                    mma16816(o[2 * np], pfrag[kk], bb[0], bb[1]);
+                    mma16816(o[2 * np + 1], pfrag[kk], bb[2], bb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // the row sums live in the 4 threads of a row
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!valid[i]) continue;
+        const float inv = 1.0f / lrow[i];
+        bf16* orow = orow0 + (size_t)(warp * 16 + g + 8 * i) * R + z0;
+#pragma unroll
+        for (int nt = 0; nt < RC / 8; ++nt) {
+            const int c = nt * 8 + 2 * q4;
+            if (c < ocols)
+                *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+        }
+    }
+}
+
+template <int KT, int RC>
+static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
+                             const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
+                             int page_size, int n_seqs, int ntok, int H, int R, int r, float scale, int window,
+                             const PageBounds pb, cudaStream_t stream) {
+    const size_t smem = (size_t)(64 + 2 * KT) * (R + r + 8) * sizeof(bf16);
+    auto kern = latent_attention_mma_kernel<KT, RC>;
+    static bool attr_set = false;                        // per instantiation
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    const long long chunks = ((long long)ntok * H + 63) / 64 + n_seqs;
+    dim3 grid((unsigned)chunks, (R + RC - 1) / RC);
+    return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qcat, (const bf16*)pool, pool_row,
+                     (bf16*)out, cu_seqlens, positions, seq_of_token, page_table, max_pages, page_size, n_seqs, H, R, r,
+                     scale * 1.4426950408889634f, window, pb);
+}
+
+// Does the tensor-core kernel take these sizes?  R and r multiples of 16, the staged tiles within shared memory.
+GG_API gg_latent_attention_mma_takes(int R, int r) {
+    if (R <= 0 || r < 0 || (R % 16) || (r % 16)) return 0;
+    return (size_t)(64 + 2 * 32) * (R + r + 8) * sizeof(bf16) <= 200 * 1024 ? 1 : 0;
+}
+
+// qcat [T, H, R + r], pool [page][page_size][pool_row], out [T, H, R], all bfloat16; cu_seqlens [n_seqs + 1].
+GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
+                               const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
+                               int page_size, int n_pages, int n_seqs, int ntok, int H, int R, int r, float scale,
+                               int window, int* status, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (!gg_latent_attention_mma_takes(R, r) || H <= 0 || (pool_row % 8) || pool_row < R + r || page_size <= 0 ||
+        (page_size % 64) || (((uintptr_t)qcat | (uintptr_t)pool | (uintptr_t)out) & 15))
+        return GG_ERR_ARG;
+    const PageBounds pb{n_pages, status};
+    const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;     // room for 64-key tiles
+#define GG_LM(KT, RC) launch_latent_mma<KT, RC>(qcat, pool, pool_row, out, cu_seqlens, positions, seq_of_token, page_table, \
+        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, stream)
+    int rc;
+    if (R <= 64) rc = wide ? GG_LM(64, 64) : GG_LM(32, 64);
+    else if (R <= 128) rc = wide ? GG_LM(64, 128) : GG_LM(32, 128);
+    else rc = wide ? GG_LM(64, 256) : GG_LM(32, 256);
+#undef GG_LM
+    return rc;
+}
+
 GG_API gg_latent_attention_checked() { return gg_debug_bounds(); }

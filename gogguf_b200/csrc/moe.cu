@@ -175,3 +175,114 @@ GG_API gg_moe_down(const void* y, int y_dtype, const void* w_d, int w_dtype, con
 #undef GG_DN
     return gg_last_error();
 }
+
+// ----------------------------------------------------------------------------- sorted form (steps of many tokens)
+// The (token, choice) pairs are grouped by expert so that each expert's rows are consecutive and one tensor-core
+// product per expert serves them:  sort (counts, offsets, a place for every pair)  ->  gather (row of place i =
+// the pair's token row, times its weight if the weight sits on the input)  ->  per expert: gate/up product,
+// activation, down product (float32 rows)  ->  combine (residual[t] += the rows of the token's pairs, k in order).
+// A row's result does not depend on its place, so the order of pairs inside an expert's range is free.
+
+// One block.  offsets[E + 1] (exclusive prefix sums of the experts' counts), place[p] for every pair.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* idx, int P, int E, int* offsets, int* place,
+                                                        int* cursor /* [E] scratch */) {
+    pdl_launch();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cursor[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cursor[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { const int c = cursor[e]; offsets[e] = run; cursor[e] = run; run += c; }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) place[p] = atomicAdd(&cursor[idx[p]], 1);
+}
+
+GG_API gg_moe_sort(const int* idx, int P, int E, int* offsets, int* place, int* cursor, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (E <= 0) return GG_ERR_ARG;
+    gg_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, 1, idx, P, E, offsets, place, cursor);
+    return gg_last_error();
+}
+
+// xs[place[p]] = bfloat16(h[p / top] * (weight_on_input ? wts[p] : 1)); one block per pair.
+__global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* h, const float* wts, const int* place, bf16* xs,
+                                                         int W, int top, int weight_on_input) {
+    pdl_launch();
+    pdl_wait();
+    const int p = blockIdx.x;
+    const float f = weight_on_input ? wts[p] : 1.0f;
+    const bf16* src = h + (size_t)(p / top) * W;
+    bf16* dst = xs + (size_t)place[p] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = __float2bfloat16_rn(__bfloat162float(src[i]) * f);
+}
+
+GG_API gg_moe_gather(const void* h, const float* wts, const int* place, void* xs, int P, int W, int top,
+                     int weight_on_input, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    gg_launch(moe_gather_kernel, dim3(P), dim3(128), 0, stream, 1, (const bf16*)h, wts, place, (bf16*)xs, W, top,
+              weight_on_input);
+    return gg_last_error();
+}
+
+// y[i, f] = out_scale * act(gu[i, f], gu[i, F + f]) (times the pair's weight if it sits on the output), rows in
+// sorted order; pair_of[i] is the pair at place i (only read when the weight is on the output).
+__global__ void moe_glu_rows_kernel(const bf16* gu, bf16* y, long long n, int F, float limit, float slope, float out_scale,
+                                    const float* wts, const int* pair_of) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long row = i / F;
+    const int f = (int)(i % F);
+    float a = clamped_glu(__bfloat162float(gu[row * 2 * F + f]), __bfloat162float(gu[row * 2 * F + F + f]), limit, slope) * out_scale;
+    if (pair_of != nullptr) a *= wts[pair_of[row]];
+    y[i] = __float2bfloat16_rn(a);
+}
+
+GG_API gg_moe_glu_rows(const void* gu, void* y, int P, int F, float limit, float slope, float out_scale,
+                       const float* wts, const int* pair_of, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    const long long n = (long long)P * F;
+    gg_launch(moe_glu_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)y, n, F,
+              limit, slope, out_scale, wts, pair_of);
+    return gg_last_error();
+}
+
+// pair_of[place[p]] = p
+__global__ void moe_invert_kernel(const int* place, int* pair_of, int P) {
+    pdl_launch();
+    pdl_wait();
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < P) pair_of[place[p]] = p;
+}
+
+GG_API gg_moe_invert(const int* place, int* pair_of, int P, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    gg_launch(moe_invert_kernel, dim3((P + 255) / 256), dim3(256), 0, stream, 1, place, pair_of, P);
+    return gg_last_error();
+}
+
+// residual[t, :] += sum_k rows[place[t * top + k], :]
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* rows, const int* place, float* residual, int W,
+                                                          int top, const int* __restrict__ seq_of_token) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) s += rows[(size_t)place[(size_t)t * top + k] * W + i];
+        residual[(size_t)t * W + i] += s;
+    }
+}
+
+GG_API gg_moe_combine(const float* rows, const int* place, float* residual, int T, int W, int top,
+                      const int* seq_of_token, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    gg_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, 1, rows, place, residual, W, top, seq_of_token);
+    return gg_last_error();
+}

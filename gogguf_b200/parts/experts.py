@@ -144,7 +144,7 @@ class RoutedExperts:
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
         idx, wts = self.route(h, ctx)
-        if self._grouped is not None and self._grouped.takes(T):
+        if self._grouped is not None and self._grouped.takes(ctx):
             self._grouped.run(h, idx, wts, residual, ctx)
             return
         y = ctx.ws.get("moe_act", (T * self.top, self.inter), torch.float32)

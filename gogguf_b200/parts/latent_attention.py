@@ -93,7 +93,7 @@ class LatentAttentionMixer:
         self._fast = None
         if rt.fast and rt.dtype == torch.bfloat16 and self.uk_t.dtype == torch.bfloat16:
             from ..csrc import fast_latent
-            self._fast = fast_latent.try_make(H, R, r, self.scale, self.window)
+            self._fast = fast_latent.try_make(H, d, R, r, self.nq + R + r, self.scale, self.window)
 
     def scale_output(self, mult: float) -> bool:
         """Multiply what this part adds to the residual by `mult`: the factor goes onto the heads' outputs in

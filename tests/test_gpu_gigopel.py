@@ -1,0 +1,388 @@
+"""The Gigopel decoder through the framework against the plain implementation (tests/plain_gigopel.py):
+whole prompts, layer by layer, decoding, portions, unequal batches, reuse of slots and pages, windows and page
+borders, other sizes, the entry point."""
+import pytest
+import torch
+
+import plain_gigopel as plain
+from gigopel_cases import CASES, make_folder, plain_logits
+from helpers import random_tokens, read_folder, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 3e-5
+TOL_BF16 = 3e-2
+
+
+def tol(dtype):
+    return TOL_F32 if dtype == "float32" else TOL_BF16
+
+
+def close(got, want, dtype, routed=True) -> bool:
+    """float32: every row within TOL_F32.  bfloat16: every row within TOL_BF16, except that in a model with routed
+    experts a few rows may differ: where two experts' scores lie closer than the rounding of the activations, the
+    bfloat16 run may take the other one, which changes that token's row by much more than rounding (and the rows
+    that read it a little).  Each kernel alone, the float32 runs and the made-up keys hold every row."""
+    got, want = got.double().cpu(), want.double().cpu()
+    scale = want.abs().max().clamp_min(1e-30)
+    rows = (got - want).abs().reshape(got.shape[0], -1).max(dim=1).values / scale
+    if dtype == "float32" or not routed:
+        return bool(rows.max() < tol(dtype))
+    bad = int((rows >= TOL_BF16).sum())
+    return bad <= max(1, got.shape[0] // 25) and float(rows.median()) < TOL_BF16 / 3
+
+
+def load(folder, dtype, fast=True, max_tokens=2048, graphs=False):
+    from gogguf_b200.engine import Model, Stepper
+    from gogguf_b200.engine.graphs import GraphStepper
+    model = Model.load(folder, dtype=dtype, fast=fast)
+    cache = model.new_cache(max_tokens=max_tokens)
+    return model, cache, (GraphStepper if graphs else Stepper)(model, cache)
+
+
+def run_cut(st, cache, tokens, cuts):
+    """One request in portions of the given sizes (the rest one token at a time); logits at every position."""
+    from gogguf_b200.engine import StepEntry
+    slot = cache.open()
+    rows, at = [], 0
+    for n in list(cuts) + [1] * (len(tokens) - sum(cuts)):
+        rows.append(st.step([StepEntry(slot, tokens[at:at + n], want=list(range(n)))]).clone())
+        at += n
+    cache.close(slot)
+    cache.check()
+    return torch.cat(rows, dim=0)
+
+
+@pytest.mark.parametrize("name", ["T", "ONE", "ODD", "W"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts_and_every_layer(tmp_path_factory, name, dtype):
+    from gogguf_b200.engine import LayerTaps, StepEntry
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
+    cfg, w = read_folder(folder)
+    model, cache, st = load(folder, dtype)
+    for n in (1, 2, 150) + ((600,) if name == "W" else ()):     # 600 tokens: the experts' sorted form in bfloat16
+        tokens = random_tokens(cfg["vocab"], n, seed=n)
+        want_layers = []
+        want = plain_logits(cfg, w, tokens, want_layers)
+        got_layers = []
+        slot = cache.open()
+        got = st.step([StepEntry(slot, tokens, want=list(range(n)))],
+                      LayerTaps(on_layer=lambda i, rows: got_layers.append(rows.clone()))).clone()
+        cache.close(slot)
+        for i, (a, b) in enumerate(zip(got_layers, want_layers)):
+            assert close(a, b, dtype), (name, n, "layer", i, rel_err(a, b))
+        assert len(got_layers) == len(cfg["layers"])
+        assert close(got, want, dtype), (name, n, rel_err(got, want))
+    if dtype == "bfloat16":
+        # the plain kernels on the same weights are the twins of the tensor-core kernels
+        _, cache2, st2 = load(folder, dtype, fast=False)
+        twin = run_cut(st2, cache2, tokens, [len(tokens)])
+        assert close(twin, want, dtype)
+        med = lambda x: float(((x.double().cpu() - want).abs().amax(1) / want.abs().max()).median())
+        assert med(got) < 1.5 * med(twin) + 2e-3
+
+
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("ONE", "float32"), ("ODD", "bfloat16"),
+                                        ("W", "bfloat16")])
+def test_portions_and_decoding_equal_the_whole_prompt(tmp_path_factory, name, dtype):
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab"], 171, seed=12)
+    want = plain_logits(cfg, w, tokens)
+    model, cache, st = load(folder, dtype)
+    for cuts in ([171], [64, 64, 43], [2, 2, 61, 3, 100], [63, 2, 70], [130]):
+        got = run_cut(st, cache, tokens, cuts)
+        assert close(got, want, dtype), (name, cuts, rel_err(got, want))
+    # token by token from the first one, through captured graphs where the model is decoded that way
+    _, cache_g, st_g = load(folder, dtype, graphs=True)
+    short = tokens[:90]
+    got = run_cut(st_g, cache_g, short, [])
+    assert close(got, want[:90], dtype), rel_err(got, want[:90])
+
+
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("W", "bfloat16"), ("ODD", "float32")])
+def test_unequal_batches_reused_slots_and_pages(tmp_path_factory, name, dtype):
+    """Requests of different lengths in one batch, decoded together while the short ones leave; the slots and
+    pages they give back are taken by the next batch (the cache is sized so that it has to reuse them)."""
+    from gogguf_b200.engine import StepEntry
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
+    cfg, w = read_folder(folder)
+    model, cache, st = load(folder, dtype, max_tokens=448, graphs=True)
+    got_rows, want_rows = [], []
+    for wave in range(3):
+        reqs = [random_tokens(cfg["vocab"], n, seed=100 * wave + n) for n in (1, 65, 130, 7)]
+        tails = [3, 20, 9, 40]
+        full = [r + random_tokens(cfg["vocab"], t, seed=7 + t + wave) for r, t in zip(reqs, tails)]
+        oracle = [plain_logits(cfg, w, f) for f in full]
+        slots = [cache.open() for _ in reqs]
+        out = st.step([StepEntry(s, r, want=[len(r) - 1]) for s, r in zip(slots, reqs)]).clone()
+        for i, r in enumerate(reqs):
+            got_rows.append(out[i]); want_rows.append(oracle[i][len(r) - 1])
+        live = list(range(len(reqs)))
+        for k in range(max(tails)):
+            live = [i for i in live if k < tails[i]]
+            ent = [StepEntry(slots[i], [full[i][len(reqs[i]) + k]], want=[0]) for i in live]
+            out = st.step(ent).clone()
+            for j, i in enumerate(live):
+                got_rows.append(out[j]); want_rows.append(oracle[i][len(reqs[i]) + k])
+            for i in live:
+                if k == tails[i] - 1:
+                    cache.close(slots[i])
+        cache.check()
+        assert cache.live_slots == 0
+    got, want = torch.stack(got_rows), torch.stack(want_rows)
+    assert close(got, want, dtype), rel_err(got, want)
+
+
+def test_long_decoding_past_every_window_and_page(tmp_path_factory):
+    """A short prompt and 300 decoded tokens in float32: windows of 7 and 70 pass over decoded tokens, windowed
+    groups give pages back and the sequence crosses four page borders."""
+    folder = make_folder(tmp_path_factory.getbasetemp(), "T", "float32")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab"], 305, seed=77)
+    want = plain_logits(cfg, w, tokens)
+    model, cache, st = load(folder, "float32", max_tokens=512, graphs=True)
+    got = run_cut(st, cache, tokens, [5])
+    err = [(rel_err(got[i], want[i]), i) for i in range(len(tokens))]
+    assert max(err)[0] < TOL_F32, max(err)
+
+
+MARKED, ASKING = 1, 5      # token ids: the one that is asked for, and the one whose query asks for it
+
+
+def _standout_model(tmp, window):
+    """A one-layer model without feed-forward whose weights make one key stand out.  The marked token's latent is
+    large along its first element and every other token's is zero there (their embeddings are made orthogonal to
+    the direction that feeds it); the first plain key element of each head copies that latent element, and the
+    asking token's query is large there.  So the asking token gives the marked one a score of about 30 and every
+    other key a score of 0: whether the marked token is visible decides the output."""
+    import os
+    from gogguf_b200.weights.loader import write_model_folder
+    W, R, d, r, dv, H, V = 64, 32, 16, 16, 16, 2, 64
+    mx = dict(heads=H, dim=d, rot_dim=r, vdim=dv, kv_rank=R, scale=1.0, rot=dict(base=10000.0, dims=r))
+    if window:
+        mx["mask"] = dict(size=window)
+    cfg = dict(architecture="Gigopel", vocab=V, width=W, residual_mult=1.0, norm=dict(eps=1e-6),
+               layers=[dict(type="latent_attention", mixer=mx, mlp=None)])
+    g = torch.Generator().manual_seed(31)
+    embed = torch.randn(V, W, generator=g)
+    a = embed[MARKED] / embed[MARKED].norm()
+    for j in range(V):
+        if j != MARKED:
+            embed[j] -= (embed[j] @ a) * a
+    m = embed[ASKING] / embed[ASKING].norm()
+    dkv = torch.randn(R + r, W, generator=g) * 0.04
+    dkv[0] = 4.0 * a
+    q = torch.zeros(H * (d + r), W)
+    uk = torch.zeros(H * d, R)
+    for h in range(H):
+        q[h * (d + r)] = (6.0 / 8.0) * m
+        uk[h * d, 0] = 1.0
+    w = {"embed": embed, "final.norm": torch.zeros(W), "l0.norm1": torch.zeros(W), "l0.mix.q": q, "l0.mix.dkv": dkv,
+         "l0.mix.dkv.norm": torch.ones(R), "l0.mix.uk": uk, "l0.mix.uv": torch.randn(H * dv, R, generator=g) * 0.3,
+         "l0.mix.o": torch.randn(W, H * dv, generator=g) * 0.3}
+    w = {k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}       # values both compute dtypes hold exactly
+    folder = os.path.join(str(tmp), f"standout_{window}")
+    if not os.path.isdir(folder):
+        write_model_folder(folder, cfg, w)
+    return folder, cfg, {k: v.float() for k, v in w.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,n", [(40, 100), (64, 130), (65, 200), (None, 700)])
+def test_keys_at_the_window_edge_at_page_borders_and_far_away(tmp_path, dtype, window, n):
+    """The marked token sits just inside the window, just outside it, at the first position, on either side of a page
+    border and (without a window) hundreds of positions back; in a prompt and in decoding."""
+    folder, cfg, w = _standout_model(tmp_path, window)
+    model, cache, st = load(folder, dtype)
+    spots = {0, 63, 64, n - 2} | ({n - window - 1, n - window, n - window + 1} if window else {n - 600, 65})
+    for marked in sorted(s for s in spots if 0 <= s < n - 1):
+        tokens = [6 + (i * 7) % 50 for i in range(n)]
+        tokens[marked], tokens[-1] = MARKED, ASKING
+        want = plain_logits(cfg, w, tokens)
+        unseen = list(tokens)
+        unseen[marked] = 7
+        base = plain_logits(cfg, w, unseen)
+        inside = window is None or (n - 1) - marked < window
+        # the test can tell: seeing the marked token or not moves the last logits by far more than the tolerance
+        moved = rel_err(want[-1], base[-1])
+        assert (moved > 0.2) == inside, (marked, moved)
+        for cuts in ([n], [n - 1], [marked + 1, n - marked - 2]):
+            if min(cuts) < 1:
+                continue
+            got = run_cut(st, cache, tokens, cuts)
+            assert close(got[[marked, n - 1]], want[[marked, n - 1]], dtype, routed=False), (window, marked, cuts)
+
+
+def test_latent_attention_kernels_agree_on_made_up_queries():
+    """The tensor-core kernel against the plain kernel and against a loop in torch, on queries that are a large
+    multiple of one cached row: the row just inside the window, just outside it, the first one, a far one."""
+    from gogguf_b200.csrc import fast_latent, kernels as K
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(5)
+    for H, R, r, window, page_rows in ((3, 48, 16, 37, 64), (16, 128, 32, 130, 64), (5, 272, 16, 0, 64), (1, 16, 16, 64, 64)):
+        D = R + r
+        n = 333
+        row = (D + 7) // 8 * 8
+        n_pages = 8
+        pool = torch.zeros(n_pages, page_rows, row)
+        pages = [5, 2, 7, 0, 3, 6]                      # the sequence's pages are not in order
+        keys = torch.randn(n, D, generator=g)
+        for j in range(n):
+            pool[pages[j // page_rows], j % page_rows, :D] = keys[j]
+        # new tokens: the last 70 positions; each head of each token asks for one row
+        T = 70
+        pos = torch.arange(n - T, n)
+        asks = torch.zeros(T, H, dtype=torch.long)
+        q = torch.zeros(T, H, D)
+        for t in range(T):
+            for h in range(H):
+                p = int(pos[t])
+                choice = [p, max(0, p - window + 1) if window else 0, max(0, p - window) if window else 1,
+                          p // 2, (p // 64) * 64, max(0, (p // 64) * 64 - 1)][(t + h) % 6]
+                asks[t, h] = choice
+                q[t, h] = keys[choice] * (12.0 / keys[choice].norm() ** 2) * 2.0
+        scale = 0.5
+        pool_b = pool.to(torch.bfloat16)
+        q_b = q.to(torch.bfloat16)
+        # the loop
+        want = torch.zeros(T, H, R, dtype=torch.float64)
+        kd = torch.stack([pool_b[pages[j // page_rows], j % page_rows, :D] for j in range(n)]).double()
+        for t in range(T):
+            p = int(pos[t])
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(H):
+                s = (kd[lo:p + 1] @ q_b[t, h].double()) * scale
+                want[t, h] = torch.softmax(s, 0) @ kd[lo:p + 1, :R]
+        ints = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        table = ints([pages + [0] * 2])
+        positions, sot, cu = ints(pos.tolist()), ints([0] * T), ints([0, T])
+        out_plain = torch.empty(T, H, R, dtype=torch.bfloat16, device=dev)
+        K.latent_attention_plain(q_b.to(dev), pool_b.to(dev), out_plain, positions, sot, table, page_rows, T, H, R, r,
+                                 scale, window)
+        assert rel_err(out_plain, want) < 8e-3
+        assert fast_latent.mma_takes(R, r)
+        out_fast = torch.full((T, H, R), float("nan"), dtype=torch.bfloat16, device=dev)
+        fast_latent.latent_attention_mma(q_b.to(dev), pool_b.to(dev), out_fast, cu, positions, sot, table, page_rows,
+                                         1, T, H, R, r, scale, window)
+        assert rel_err(out_fast, want) < 8e-3, (H, R, r, window)
+        # the same tokens as 70 sequences of one token each (a decode step), with padding sequences between them
+        B = 2 * T
+        cu2 = ints(list(range(B + 1)))
+        sot2 = ints([i // 2 if i % 2 == 0 else -1 for i in range(B)])
+        pos2 = ints([int(pos[i // 2]) if i % 2 == 0 else 0 for i in range(B)])
+        table2 = ints([pages + [0] * 2] * B)             # one row per sequence of the step, padding ones included
+        q2 = torch.zeros(B, H, D, dtype=torch.bfloat16)
+        q2[0::2] = q_b
+        out2 = torch.full((B, H, R), float("nan"), dtype=torch.bfloat16, device=dev)
+        fast_latent.latent_attention_mma(q2.to(dev), pool_b.to(dev), out2, cu2, pos2, sot2, table2, page_rows,
+                                         B, B, H, R, r, scale, window)
+        assert rel_err(out2[0::2], want) < 8e-3
+        assert torch.equal(out2[1::2].float().cpu(), torch.zeros(T, H, R))
+
+
+def test_per_head_products_on_the_tensor_cores_equal_the_plain_ones():
+    from gogguf_b200.csrc import fast_latent, kernels as K
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(6)
+    for H, N, Kd, M in ((3, 48, 24, 77), (16, 128, 32, 1), (4, 40, 272, 130), (1, 16, 16, 64)):
+        ldx, hx = H * (Kd + 8) + 16, Kd + 8
+        x = torch.randn(M, ldx, generator=g).to(torch.bfloat16)
+        w = (torch.randn(H, N, Kd, generator=g) * 0.2).to(torch.bfloat16)
+        xh = torch.stack([x[:, h * hx:h * hx + Kd] for h in range(H)], 1).double()        # [M, H, K]
+        want = 0.7 * torch.einsum("mhk,hnk->mhn", xh, w.double())
+        for fn in (K.headwise_gemm, fast_latent.headwise_gemm_mma):
+            for odt in (torch.bfloat16, torch.float32):
+                out = torch.zeros(M, H, N + 8, dtype=odt, device=dev)
+                fn(x.to(dev), ldx, hx, w.to(dev), out, H * (N + 8), N + 8, M, alpha=0.7)
+                assert rel_err(out[:, :, :N], want) < (8e-3 if odt == torch.bfloat16 else 1e-5), (fn.__name__, H, N, Kd, M)
+                assert float(out[:, :, N:].abs().max()) == 0.0
+
+
+def test_xielu_router_and_experts_alone():
+    """The activation on both sides of zero and far from it; the router with ties and several choices; the
+    experts through the index against the plain expert, weight on the input and clamps in play."""
+    from gogguf_b200.csrc import kernels as K
+    dev = torch.device("cuda:0")
+    z = torch.tensor([-30.0, -4.0, -1.0, -1e-4, 0.0, 1e-4, 0.5, 3.0, 20.0], device=dev)
+    p, q = torch.tensor(0.3), torch.tensor(-0.8)
+    out = torch.empty_like(z)
+    K.xielu(z, out, float(plain.softplus(p.double())), float(0.5 + plain.softplus(q.double())), 0.6)
+    assert rel_err(out, 0.6 * plain.xielu(z.double().cpu(), p, q)) < 1e-6
+    # router: rows with ties (the lower index wins), top 3 of 7
+    logits = torch.tensor([[0.1, 2.0, 2.0, -1.0, 2.0, 0.3, 0.2], [5.0, -5.0, 0.0, 0.0, 1.0, 1.0, 1.0]], device=dev)
+    idx = torch.empty(2, 3, dtype=torch.int32, device=dev)
+    wts = torch.empty(2, 3, dtype=torch.float32, device=dev)
+    K.moe_route(logits, 3, idx, wts, None)
+    assert idx.tolist() == [[1, 2, 4], [0, 4, 5]]
+    assert rel_err(wts, torch.sigmoid(torch.gather(logits, 1, idx.long()))) < 1e-6
+    K.moe_route(logits, 3, idx, wts, None, softmax=True, renormalize=True)
+    sm = torch.softmax(logits, 1).gather(1, idx.long())
+    assert rel_err(wts, sm / sm.sum(1, keepdim=True)) < 1e-6
+    # experts through the index
+    g = torch.Generator(device="cpu").manual_seed(2)
+    T, W, F, E, top, limit = 9, 40, 24, 5, 2, 0.5
+    t = {f"e{e}.{n}": torch.randn(*s, generator=g) * 0.4 for e in range(E)
+         for n, s in (("gate", (F, W)), ("up", (F, W)), ("down", (W, F)))}
+    h = torch.randn(T, W, generator=g)
+    ch = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    wt = torch.rand(T, top, generator=g) + 0.2
+    want = torch.zeros(T, W, dtype=torch.float64)
+    for i in range(T):
+        for k in range(top):
+            e = int(ch[i, k])
+            want[i] += 0.3 * plain.expert((wt[i, k] * h[i]).double()[None], t, f"e{e}.", limit)[0]
+    w_gu = torch.stack([torch.stack([t[f"e{e}.gate"], t[f"e{e}.up"]]) for e in range(E)]).to(dev)
+    w_d = torch.stack([t[f"e{e}.down"] for e in range(E)]).to(dev)
+    y = torch.empty(T * top, F, device=dev)
+    res = torch.zeros(T, W, device=dev)
+    K.moe_gate_up(h.to(dev), w_gu, ch.to(dev), wt.to(dev), y, T, top, True, limit, 1.702, 0.3)
+    K.moe_down(y, w_d, ch.to(dev), res, T, top, None)
+    assert rel_err(res, want) < 1e-5
+    assert float((torch.einsum("tw,efw->tef", h, torch.stack([t[f"e{e}.gate"] for e in range(E)])).abs() > limit)
+                 .float().mean()) > 0.05          # the clamp is in play
+
+
+def test_experts_sorted_form_equals_the_form_through_the_index(tmp_path_factory, monkeypatch):
+    from gogguf_b200.parts import experts_grouped
+    folder = make_folder(tmp_path_factory.getbasetemp(), "W", "bfloat16")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab"], 700, seed=4)
+    model, cache, st = load(folder, "bfloat16")
+    assert all(b.feed_forward._grouped is not None for b in model.blocks if hasattr(b.feed_forward, "_grouped"))
+    sorted_form = run_cut(st, cache, tokens, [700])
+    monkeypatch.setattr(experts_grouped, "MIN_PAIRS", 1 << 30)
+    through_index = run_cut(st, cache, tokens, [700])
+    assert not torch.equal(sorted_form, through_index)          # two routes
+    assert close(sorted_form, through_index, "bfloat16")
+    assert close(sorted_form, plain_logits(cfg, w, tokens), "bfloat16")
+
+
+def test_greedy_generation_through_the_entry_point(tmp_path_factory):
+    import gogguf_b200 as gg
+    for name, dtype in (("T", "float32"), ("W", "bfloat16")):
+        folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype, std=0.3 if dtype == "float32" else 0.12)
+        cfg, w = read_folder(folder)
+        prompts = [random_tokens(cfg["vocab"], n, 30 + n) for n in (5, 1, 80)]
+        engine = gg.load(folder, gg.LoadOptions(dtype=dtype, max_tokens=1024))
+        ctx = engine.new_context()
+        out = ctx.generate(prompts, gg.GenerateParams(max_tokens=12, stop_token_ids=[], keep_logits=True))
+        rows, refs = [], []
+        for p, r in zip(prompts, out):
+            assert len(r.tokens) == 12 and r.prompt_tokens == len(p) and len(r.logits) == 12
+            whole = plain_logits(cfg, w, list(p) + r.tokens[:-1])
+            for k, row in enumerate(r.logits):
+                assert int(row.argmax()) == r.tokens[k]            # greedy: the token is the best of its own row
+                rows.append(row)
+                refs.append(whole[len(p) - 1 + k])
+        assert close(torch.stack(rows), torch.stack(refs), dtype)
+        if dtype == "float32":
+            seq = list(prompts[0])
+            for tok in out[0].tokens[:6]:
+                assert tok == int(plain_logits(cfg, w, seq)[-1].argmax())
+                seq.append(tok)
+        # a second round in the same context reuses the slots and pages the first gave back
+        again = ctx.generate(prompts, gg.GenerateParams(max_tokens=12, stop_token_ids=[]))
+        assert [r.tokens for r in again] == [r.tokens for r in out]
+        ctx.cache.check()
+        assert ctx.cache.live_slots == 0
