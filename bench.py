@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024] [--decode-contexts 16384,32768]
+    python bench.py --compare gigopel [--compare-sizes 2k,4k]      (another workload, see the end of this text)
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -20,6 +21,12 @@ launching stream.  One JSON line is printed:
   workload     (--workload) the shape's own request mix through Context.generate: prefill and decode rates
   prefill_sweep_ms  (--prefill-lengths) one prefill step per listed prompt length
   decode_by_context (--decode-contexts) decode steps of sequences that already hold that many tokens
+
+`--compare gigopel` leaves all of the above aside and measures the Gigopel design (latent attention in a sliding
+window, parallel blocks, xIELU or routed-expert feed-forwards) beside Qwen3 at equal width, depth, head count
+and feed-forward parameter count (Qwen3 with full attention), random weights: one prefill step of 2,048 tokens and decode steps at batch
+8 and 64 from 2,048-token contexts, for an all-dense and an all-experts Gigopel model per size.  It prints one JSON
+line {"compare": "gigopel", "sizes": {...}} and per-model lines on stderr.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
@@ -146,6 +153,163 @@ def prefill_flops(c, layers, t):
     return gemm + attn
 
 
+# ----------------------------------------------------------------------------- --compare gigopel
+# layer sizes that resemble real models of this kind (8 layers each, so that a model is a few GB)
+GIGOPEL_SIZES = {
+    "2k": dict(width=2048, heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=256, window=1024, ff=8192,
+               experts=16, top=2, expert_ff=1024, layers=8, vocab=65536),
+    "4k": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, window=2048, ff=16384,
+               experts=32, top=4, expert_ff=2048, layers=8, vocab=65536),
+}
+
+
+def gigopel_config(z, kind):
+    mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+                 scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=dict(base=250000.0, dims=z["rot_dim"]),
+                 mask=dict(size=z["window"]))
+    mlp = dict(kind="dense", ff=z["ff"]) if kind == "dense" else dict(
+        kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"]))
+    return dict(architecture="Gigopel", vocab=z["vocab"], width=z["width"], residual_mult=0.5, norm=dict(eps=1e-6),
+                initializer_range=0.02,
+                layers=[dict(type="latent_attention", mixer=mixer, mlp=mlp) for _ in range(z["layers"])])
+
+
+def qwen3_like(z):
+    """Qwen3 at the same width, depth, head count and feed-forward parameter count (3 matrices instead of 2), with
+    full attention (its cache of a 2,048-token context is read whole; Gigopel reads its window)."""
+    inter = (2 * z["ff"] // 3) // 128 * 128
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=z["layers"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=8, head_dim=128,
+                intermediate_size=inter, vocab_size=z["vocab"], rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=True, max_position_embeddings=8192, initializer_range=0.02)
+
+
+def compare_run(a):
+    import torch
+    from gogguf_b200.config import config_from_dict
+    from gogguf_b200.csrc import build, tcgen05_gemm
+    from gogguf_b200.engine import Model, StepEntry
+    from gogguf_b200.engine.graphs import GraphStepper
+    from gogguf_b200.sampling import Sampler, SamplerConfig
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    g = torch.Generator().manual_seed(0)
+
+    def rand_tokens(V, n):
+        return torch.randint(0, V, (n,), generator=g).tolist()
+
+    def prefill_ms(model, n):
+        cache = model.new_cache(n + 64)
+        st = GraphStepper(model, cache)
+        times = []
+        for it in range(4):
+            s = cache.open()
+            toks = rand_tokens(model.vocab_size, n)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            n0 = build.launch_count()
+            ev0.record()
+            st.step([StepEntry(s, toks, want=[n - 1])])
+            ev1.record()
+            torch.cuda.synchronize()
+            times.append(ev0.elapsed_time(ev1))
+            launches = build.launch_count() - n0
+            cache.close(s)
+        return sorted(times[1:])[1], launches
+
+    def decode_ms(model, batch, prompt_len, steps, warmup):
+        room = prompt_len + warmup + steps + 8
+        cache = model.new_cache(batch * (-(-room // 64) * 64))
+        st = GraphStepper(model, cache)
+        slots = [cache.open() for _ in range(batch)]
+        chunk = max(1, 8192 // prompt_len)
+        last = []
+        for i in range(0, batch, chunk):
+            ents = [StepEntry(s, rand_tokens(model.vocab_size, prompt_len), want=[prompt_len - 1]) for s in slots[i:i + chunk]]
+            last.append(st.step(ents).clone())
+        sampler = Sampler(SamplerConfig())
+        rows = list(range(batch))
+        pending = sampler.sample_async(torch.cat(last), rows, [0] * batch)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(warmup + steps):
+            if it == warmup:
+                pending.tokens()
+                torch.cuda.synchronize()
+                ev0.record()
+            logits = st.decode_from_device(slots, pending.device_tokens, rows)
+            nxt = sampler.sample_async(logits, rows, [it + 1] * batch)
+            pending.tokens()
+            pending = nxt
+        ev1.record()
+        torch.cuda.synchronize()
+        tcgen05_gemm.check_status(dev)
+        kernels = getattr(st, "last_graph_kernels", 0)
+        for s in slots:
+            cache.close(s)
+        return ev0.elapsed_time(ev1) / steps, kernels
+
+    def gig_numbers(z, kind, t):
+        """Floating-point operations of a prefill step of t tokens and bytes a decode step reads, per layer stack."""
+        W, H, d, r, dv, R, win = z["width"], z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], z["window"]
+        mats = H * (d + r) * W + (R + r) * W + H * (d + dv) * R + W * H * dv
+        ff_active = 2 * W * z["ff"] if kind == "dense" else z["top"] * 3 * W * z["expert_ff"] + z["experts"] * W
+        keys = sum(min(i + 1, win) for i in range(t))
+        attn = 2 * H * (2 * R + r) * keys                      # absorbed form: scores over R + r, values over R
+        flops = z["layers"] * (2 * t * (mats + ff_active) + attn) + 2 * z["vocab"] * W
+        ff_read = 2 * W * z["ff"] if kind == "dense" else z["experts"] * 3 * W * z["expert_ff"]
+        return flops, z["layers"] * (mats + ff_read) * 2 + z["vocab"] * W * 2
+
+    def qwen_numbers(c, z, t):
+        qw, kvw, h, i = c["num_attention_heads"] * 128, 8 * 128, c["hidden_size"], c["intermediate_size"]
+        mats = (qw + 2 * kvw) * h + h * qw + 3 * h * i
+        keys = t * (t + 1) // 2
+        flops = z["layers"] * (2 * t * mats + 2 * 2 * qw * keys) + 2 * z["vocab"] * h
+        return flops, z["layers"] * mats * 2 + z["vocab"] * h * 2
+
+    out = {}
+    T = PROMPT_LEN
+    for name in [x for x in a.compare_sizes.split(",") if x.strip()]:
+        z = GIGOPEL_SIZES[name]
+        arms = [("gigopel_dense", gigopel_config(z, "dense")), ("gigopel_experts", gigopel_config(z, "moe")),
+                ("qwen3_like", qwen3_like(z))]
+        res = {}
+        for arm, cd in arms:
+            cfg = config_from_dict(cd)
+            model = Model.random(cfg, seed=3, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
+            torch.cuda.synchronize()
+            flops, wbytes = qwen_numbers(cd, z, T) if arm == "qwen3_like" else gig_numbers(z, "dense" if arm.endswith("dense") else "moe", T)
+            pms, launches = prefill_ms(model, T)
+            r = {"params_b": round(cfg.parameter_count() / 1e9, 3), "prefill_ms": round(pms, 3),
+                 "prefill_tok_s": round(T / (pms / 1e3)), "prefill_tflops": round(flops / (pms / 1e3) / 1e12, 1),
+                 "prefill_frac_of_bf16_peak": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                 "prefill_launches": launches}
+            for b in (8, 64):
+                dms, kernels = decode_ms(model, b, T, max(16, min(a.steps, 64)), max(a.warmup, 3))
+                # experts: a step reads at most batch * top experts' matrices, not all of them
+                rb = wbytes
+                if arm == "gigopel_experts":
+                    used = min(z["experts"], b * z["top"])
+                    rb -= z["layers"] * (z["experts"] - used) * 3 * z["width"] * z["expert_ff"] * 2
+                if arm == "qwen3_like":
+                    rb += b * T * 2 * z["layers"] * 8 * 128 * 2
+                else:
+                    rb += b * min(T, z["window"]) * z["layers"] * (z["kv_rank"] + z["rot_dim"]) * 2
+                r[f"decode_b{b}_ms"] = round(dms, 4)
+                r[f"decode_b{b}_tok_s"] = round(b / (dms / 1e3), 1)
+                r[f"decode_b{b}_hbm_frac"] = round(rb / (dms / 1e3) / 1e9 / pk["hbm_gbs"], 3)
+                r[f"decode_b{b}_kernels"] = kernels
+            res[arm] = r
+            print(f"[bench] {name} {arm}: {r}", file=sys.stderr)
+            del model
+            torch.cuda.empty_cache()
+        out[name] = res
+    print(json.dumps({"compare": "gigopel", "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), seeded token ids",
+                      "prompt_len": T, "peaks": pk["source"], "sizes": out}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,8 +331,13 @@ def main():
                     "decode_by_context)")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
+    ap.add_argument("--compare", default="", choices=["", "gigopel"],
+                    help="another workload: the named design beside Qwen3 at equal size (prefill and decode), see the top")
+    ap.add_argument("--compare-sizes", default="2k,4k", help="which of the comparison's layer sizes to run")
     a = ap.parse_args()
 
+    if a.compare:
+        return compare_run(a)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "magomedcoder/gogguf is a Go program; no Go toolchain and no network here, pip cannot install it"}))

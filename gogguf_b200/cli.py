@@ -131,7 +131,7 @@ def cmd_info(a) -> int:
     cfg, tensors = _folder_summary(a.m)
     d = cfg.to_dict()
     print(f"Folder: {a.m}")
-    print(f"Architecture: {d.get('architectures', ['?'])[0]}")
+    print(f"Architecture: {(d.get('architectures') or [d.get('architecture', '?')])[0]}")
     print(f"Tensors: {len(tensors)}")
     print(f"Weights size: {sum(t[3] for t in tensors) / 1e6:.1f} MB")
     if hasattr(cfg, "parameter_count"):

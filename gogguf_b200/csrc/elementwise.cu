@@ -496,9 +496,34 @@ __global__ void xielu_kernel(const T* z, T* out, float ap, float aq, float out_s
     out[idx] = from_f<T>(f * out_scale);
 }
 
+// The same for bfloat16 with eight elements (16 bytes) per thread.
+__global__ void __launch_bounds__(256) xielu_vec8_kernel(const bf16* z, bf16* out, float ap, float aq, float out_scale,
+                                                         long long nvec) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    uint4 raw = reinterpret_cast<const uint4*>(z)[i];
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 v = __bfloat1622float2(h2[j]);
+        v.x = (v.x > 0.f ? fmaf(ap * v.x, v.x, 0.5f * v.x) : fmaf(aq, expm1f(v.x) - v.x, 0.5f * v.x)) * out_scale;
+        v.y = (v.y > 0.f ? fmaf(ap * v.y, v.y, 0.5f * v.y) : fmaf(aq, expm1f(v.y) - v.y, 0.5f * v.y)) * out_scale;
+        h2[j] = __floats2bfloat162_rn(v.x, v.y);
+    }
+    reinterpret_cast<uint4*>(out)[i] = raw;
+}
+
 GG_API gg_xielu(const void* z, int dtype, void* out, float ap, float aq, float out_scale, long long n,
                 cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (dtype == GG_BF16 && (n % 8) == 0 && ((((uintptr_t)z) | ((uintptr_t)out)) & 15) == 0) {
+        const long long nvec = n / 8;
+        gg_launch(xielu_vec8_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, 1, (const bf16*)z, (bf16*)out,
+                  ap, aq, out_scale, nvec);
+        return gg_last_error();
+    }
     GG_DISPATCH_DTYPE(dtype, T,
         gg_launch(xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const T*)z, (T*)out, ap, aq, out_scale, n));
     return gg_last_error();

@@ -25,7 +25,10 @@ def headwise_gemm_mma(x: torch.Tensor, ldx: int, hx: int, w: torch.Tensor, out: 
 def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
                          positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
                          page_size: int, n_seqs: int, n_tokens: int, heads: int, R: int, r: int, scale: float,
-                         window: int) -> None:
+                         window: int, splits: int = 1, part_o: Optional[torch.Tensor] = None,
+                         part_ml: Optional[torch.Tensor] = None) -> None:
+    """splits > 1 cuts every CTA's range of cached positions into that many shares (steps with few CTAs); part_o
+    float32 [n_tokens * heads, splits, R] and part_ml [n_tokens * heads, splits, 2] take the partial results."""
     for t in (qcat, pool, out):
         if t.dtype != torch.bfloat16:
             raise KernelError("latent_attention_mma takes bfloat16 queries, cache and output")
@@ -33,8 +36,14 @@ def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tens
     kernel("latent_attention", "gg_latent_attention_mma")(
         qcat.data_ptr(), pool.data_ptr(), pool.shape[-1], out.data_ptr(), cu_seqlens.data_ptr(), positions.data_ptr(),
         seq_of_token.data_ptr(), page_table.data_ptr(), page_table.shape[-1], int(page_size), pool.shape[0],
-        int(n_seqs), int(n_tokens), heads, R, r, float(scale), int(window), status_word(qcat.device).data_ptr(),
-        torch.cuda.current_stream().cuda_stream)
+        int(n_seqs), int(n_tokens), heads, R, r, float(scale), int(window), int(splits),
+        part_o.data_ptr() if part_o is not None else 0, part_ml.data_ptr() if part_ml is not None else 0,
+        status_word(qcat.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
+def mma_splits(n_seqs: int, n_tokens: int, heads: int, R: int, r: int, window: int, max_ctx: int) -> int:
+    return int(module("latent_attention").lib.gg_latent_attention_mma_splits(
+        int(n_seqs), int(n_tokens), heads, R, r, int(window), int(max_ctx)))
 
 
 def mma_takes(R: int, r: int) -> bool:
@@ -51,8 +60,15 @@ class _Fast:
         headwise_gemm_mma(qd, ldx, hx, uk_t, qcat, self.H * D, D, m)
 
     def attention(self, qcat, pool, out, ctx, table, page_size: int) -> None:
+        T, H, R = ctx.n_tokens, self.H, self.R
+        # ctx.max_ctx is the longest sequence of the step (an upper bound under a captured graph)
+        splits = mma_splits(ctx.n_seqs, T, H, R, self.r, self.window, max(int(ctx.max_ctx), 1))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = ctx.ws.get("lat_part_o", (T * H, splits, R), torch.float32)
+            part_ml = ctx.ws.get("lat_part_ml", (T * H, splits, 2), torch.float32)
         latent_attention_mma(qcat, pool, out, ctx.cu_seqlens, ctx.positions, ctx.seq_of_token, table, page_size,
-                             ctx.n_seqs, ctx.n_tokens, self.H, self.R, self.r, self.scale, self.window)
+                             ctx.n_seqs, T, H, R, self.r, self.scale, self.window, splits, part_o, part_ml)
 
     def expand(self, olat: torch.Tensor, uv: torch.Tensor, av: torch.Tensor, m: int, alpha: float) -> None:
         """av[t, h, :] = alpha * Wuv_h olat[t, h]."""

@@ -403,7 +403,8 @@ template <int KT, int RC>
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const bf16* qcat, const bf16* pool, int pool_row, bf16* out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
-    int max_pages, int page_size, int n_seqs, int H, int R, int r, float scale_log2, int window, const PageBounds pb) {
+    int max_pages, int page_size, int n_seqs, int H, int R, int r, float scale_log2, int window, const PageBounds pb,
+    float* part_o, float* part_ml) {
     pdl_launch();
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = R + r, LD = D + 8;
@@ -437,34 +438,45 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const int pos0 = positions[t0 + tl0], pos1 = pos0 + (tl1 - tl0);
     int key_lo = 0;
     if (window > 0 && pos0 - window + 1 > 0) key_lo = pos0 - window + 1;
-    const int tile0 = key_lo / KT, ntiles = pos1 / KT - tile0 + 1;
+    int tile0 = key_lo / KT, ntiles = pos1 / KT - tile0 + 1;
+    // gridDim.z > 1: the CTAs of one (rows, columns) share the range of tiles between them and leave partial sums
+    const int splits = gridDim.z, split = blockIdx.z;
+    if (splits > 1) {
+        const int per = (ntiles + splits - 1) / splits;
+        tile0 += split * per;
+        ntiles = max(0, min(per, ntiles - split * per));
+    }
     const int* pt = page_table + (size_t)b * max_pages;
     const int chunks_per_row = D / 8;
 
+    // a warp copies whole rows (one page look-up per row and lane), its lanes the rows' 16-byte pieces
     auto load_keys = [&](int tile, int stage) {
         bf16* dst = ks + (size_t)stage * KT * LD;
         const int j0 = tile * KT;
-        for (int c = tid; c < KT * chunks_per_row; c += 128) {
-            const int kk = c / chunks_per_row, col = (c % chunks_per_row) * 8;
+        for (int kk = warp; kk < KT; kk += 4) {
             const int j = j0 + kk;
-            bf16* d = dst + kk * LD + col;
+            bf16* d = dst + kk * LD;
             if (j <= pos1) {
                 const int page = gg_page(pt, j / page_size, max_pages, pb, 51);
-                cp_async16(d, pool + ((size_t)page * page_size + (j % page_size)) * pool_row + col);
+                const bf16* src = pool + ((size_t)page * page_size + (j % page_size)) * pool_row;
+                for (int c = lane; c < chunks_per_row; c += 32) cp_async16(d + c * 8, src + c * 8);
             } else {
-                zero16(d);
+                for (int c = lane; c < chunks_per_row; c += 32) zero16(d + c * 8);
             }
         }
     };
     {   // the queries of this CTA: rows_here consecutive rows of qcat
         const bf16* qsrc = qcat + ((size_t)t0 * H + f0) * D;
-        for (int c = tid; c < 64 * chunks_per_row; c += 128) {
-            const int row = c / chunks_per_row, col = (c % chunks_per_row) * 8;
-            bf16* d = qs + row * LD + col;
-            if (row < rows_here) cp_async16(d, qsrc + (size_t)row * D + col); else zero16(d);
+        for (int row = warp; row < 64; row += 4) {
+            bf16* d = qs + row * LD;
+            if (row < rows_here) {
+                for (int c = lane; c < chunks_per_row; c += 32) cp_async16(d + c * 8, qsrc + (size_t)row * D + c * 8);
+            } else {
+                for (int c = lane; c < chunks_per_row; c += 32) zero16(d + c * 8);
+            }
         }
     }
-    load_keys(tile0, 0);
+    if (ntiles > 0) load_keys(tile0, 0);
     cp_async_commit();
 
     const int g = lane >> 2, q4 = lane & 3;
@@ -495,6 +507,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         }
         __syncthreads();
         const bf16* kt = ks + (size_t)(it & 1) * KT * LD;
+        if (warp * 16 < rows_here) {                     // a warp without rows (decode steps of few heads) only copies
         float s[KT / 8][4];
 #pragma unroll
         for (int i = 0; i < KT / 8; ++i)
@@ -564,13 +577,34 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
                 }
             }
         }
+        }
         __syncthreads();
     }
+    cp_async_wait<0>();
     // the row sums live in the 4 threads of a row
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
+    }
+    if (splits > 1) {
+        // partial result of this share of the keys: unnormalised sums, the running maximum (log2 units) and the sum
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;
+            const size_t row = (size_t)t0 * H + f0 + warp * 16 + g + 8 * i;
+            float* po = part_o + (row * splits + split) * R + z0;
+#pragma unroll
+            for (int nt = 0; nt < RC / 8; ++nt) {
+                const int c = nt * 8 + 2 * q4;
+                if (c < ocols) *reinterpret_cast<float2*>(po + c) = make_float2(o[nt][2 * i], o[nt][2 * i + 1]);
+            }
+            if (q4 == 0 && blockIdx.y == 0) {
+                part_ml[(row * splits + split) * 2] = mrow[i];
+                part_ml[(row * splits + split) * 2 + 1] = lrow[i];
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -590,7 +624,7 @@ template <int KT, int RC>
 static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                              const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                              int page_size, int n_seqs, int ntok, int H, int R, int r, float scale, int window,
-                             const PageBounds pb, cudaStream_t stream) {
+                             const PageBounds pb, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
     const size_t smem = (size_t)(64 + 2 * KT) * (R + r + 8) * sizeof(bf16);
     auto kern = latent_attention_mma_kernel<KT, RC>;
     static bool attr_set = false;                        // per instantiation
@@ -600,10 +634,48 @@ static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, v
         attr_set = true;
     }
     const long long chunks = ((long long)ntok * H + 63) / 64 + n_seqs;
-    dim3 grid((unsigned)chunks, (R + RC - 1) / RC);
+    dim3 grid((unsigned)chunks, (R + RC - 1) / RC, splits);
     return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qcat, (const bf16*)pool, pool_row,
                      (bf16*)out, cu_seqlens, positions, seq_of_token, page_table, max_pages, page_size, n_seqs, H, R, r,
-                     scale * 1.4426950408889634f, window, pb);
+                     scale * 1.4426950408889634f, window, pb, part_o, part_ml);
+}
+
+// Merge of the partial results of a split: one block per (token, head) row.
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out,
+                                                             const int* __restrict__ seq_of_token, int H, int R, int splits) {
+    pdl_launch();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    if (seq_of_token[row / H] < 0) return;               // the attention kernel wrote the zero rows of padding itself
+    const float* ml = part_ml + row * splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M) * ml[2 * s + 1];
+    const float inv = 1.0f / L;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = ml[2 * s];
+            if (m != -INFINITY) acc = fmaf(exp2f(m - M), part_o[(row * splits + s) * R + c], acc);
+        }
+        out[row * R + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// How many shares of the keys a step's attention is cut into: 1 unless the step has too few CTAs to fill the
+// GPU (decode steps of small batches); bounded by the tiles a window holds and by `max_splits`.
+GG_API gg_latent_attention_mma_splits(int n_seqs, int ntok, int H, int R, int r, int window, int max_ctx) {
+    const long long ctas = (((long long)ntok * H + 63) / 64 + n_seqs) * ((R + 255) / 256);
+    if (ctas >= 148) return 1;
+    const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;
+    const int kt = wide ? 64 : 32;
+    const int keys = window > 0 && window < max_ctx ? window + 1 : max_ctx;
+    const int tiles = (keys + kt - 1) / kt + 1;
+    long long s = (2 * 148 + ctas - 1) / ctas;
+    if (s > tiles) s = tiles;
+    if (s > 32) s = 32;
+    return s < 1 ? 1 : (int)s;
 }
 
 // Does the tensor-core kernel take these sizes?  R and r multiples of 16, the staged tiles within shared memory.
@@ -613,10 +685,12 @@ GG_API gg_latent_attention_mma_takes(int R, int r) {
 }
 
 // qcat [T, H, R + r], pool [page][page_size][pool_row], out [T, H, R], all bfloat16; cu_seqlens [n_seqs + 1].
+// splits > 1: part_o [T * H, splits, R] and part_ml [T * H, splits, 2] (float32) take the shares' partial results
+// and a second kernel merges them.
 GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                                const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                                int page_size, int n_pages, int n_seqs, int ntok, int H, int R, int r, float scale,
-                               int window, int* status, cudaStream_t stream) {
+                               int window, int splits, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_latent_attention_mma_takes(R, r) || H <= 0 || (pool_row % 8) || pool_row < R + r || page_size <= 0 ||
         (page_size % 64) || (((uintptr_t)qcat | (uintptr_t)pool | (uintptr_t)out) & 15))
@@ -624,13 +698,16 @@ GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row,
     const PageBounds pb{n_pages, status};
     const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;     // room for 64-key tiles
 #define GG_LM(KT, RC) launch_latent_mma<KT, RC>(qcat, pool, pool_row, out, cu_seqlens, positions, seq_of_token, page_table, \
-        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, stream)
+        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, splits, part_o, part_ml, stream)
+    if (splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr))) return GG_ERR_ARG;
     int rc;
     if (R <= 64) rc = wide ? GG_LM(64, 64) : GG_LM(32, 64);
     else if (R <= 128) rc = wide ? GG_LM(64, 128) : GG_LM(32, 128);
     else rc = wide ? GG_LM(64, 256) : GG_LM(32, 256);
 #undef GG_LM
-    return rc;
+    if (rc != 0 || splits == 1) return rc;
+    return gg_launch(latent_combine_kernel, dim3((unsigned)(ntok * H)), dim3(128), 0, stream, 1, (const float*)part_o,
+                     (const float*)part_ml, (bf16*)out, seq_of_token, H, R, splits);
 }
 
 GG_API gg_latent_attention_checked() { return gg_debug_bounds(); }

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -148,14 +148,119 @@ def sample(ms, V: int = 151936) -> None:
             print(f"sample B={B:4d} V={V} {name:34s} {us:8.1f} us", flush=True)
 
 
+def _peaks():
+    import json
+    import os
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def latent(sizes=((16, 64, 32, 64, 256, 1024, 2048), (32, 128, 64, 128, 512, 2048, 4096))) -> None:
+    """The kernels of latent attention and of the routed experts alone, at layer sizes (heads, plain, rotated, value,
+    latent, window, width): attention in a prompt of 2,048 tokens (tensor rate) and in decode steps (cache stream),
+    the per-head products, the prep kernel, the activation, the experts through the index."""
+    from . import fast_latent as FL
+    from . import kernels as K
+    dev = "cuda:0"
+    hbm, tf, of = _peaks()
+    ints = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    for H, d, r, dv, R, win, W in sizes:
+        D = R + r
+        tag = f"H={H} R={R} r={r} window={win}"
+        # ---- a prompt of 2,048 tokens of one sequence
+        T = 2048
+        pages = T // 64
+        pool = (torch.randn(pages, 64, D, device=dev) * 0.5).to(torch.bfloat16)
+        qcat = (torch.randn(T, H, D, device=dev) * 0.2).to(torch.bfloat16)
+        olat = torch.empty(T, H, R, device=dev, dtype=torch.bfloat16)
+        table, cu = ints([list(range(pages))]), ints([0, T])
+        pos, sot = ints(list(range(T))), ints([0] * T)
+        us = _time_graph(lambda i: FL.latent_attention_mma(qcat, pool, olat, cu, pos, sot, table, 64, 1, T, H, R, r, 0.1, win), 10)
+        keys = sum(min(i + 1, win) for i in range(T))
+        fl = 2 * H * (2 * R + r) * keys
+        print(f"latent_attention_mma prompt 2048  {tag}: {us:9.1f} us {fl / us / 1e6:7.1f} TFLOP/s {fl / us / 1e6 / tf:5.3f} of {of} bf16 peak", flush=True)
+        qd = (torch.randn(T, H * (d + r) + D, device=dev) * 0.2).to(torch.bfloat16)
+        uk_t = (torch.randn(H, R, d, device=dev) * 0.1).to(torch.bfloat16)
+        uv = (torch.randn(H, dv, R, device=dev) * 0.1).to(torch.bfloat16)
+        av = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        for m in (T, 8):
+            us = _time_graph(lambda i: FL.headwise_gemm_mma(qd, qd.shape[1], d + r, uk_t, qcat, H * D, D, m), 10)
+            fl = 2 * m * H * d * R
+            by = H * d * R * 2 + m * H * (d + R) * 2
+            print(f"headwise absorb M={m:5d} {tag}: {us:9.1f} us {fl / us / 1e6:7.1f} TFLOP/s {by / us / 1e3:7.1f} GB/s", flush=True)
+            us = _time_graph(lambda i: FL.headwise_gemm_mma(olat, H * R, R, uv, av, H * dv, dv, m, 0.5), 10)
+            fl = 2 * m * H * dv * R
+            by = H * dv * R * 2 + m * H * (dv + R) * 2
+            print(f"headwise expand M={m:5d} {tag}: {us:9.1f} us {fl / us / 1e6:7.1f} TFLOP/s {by / us / 1e3:7.1f} GB/s", flush=True)
+        normw = torch.ones(R, device=dev)
+        cos, sin = torch.ones(T, r // 2, device=dev), torch.zeros(T, r // 2, device=dev)
+        us = _time_graph(lambda i: K.latent_prep(qd[:, :H * (d + r)], qd[:, H * (d + r):], normw, 1e-6, cos, sin, r, pos, sot,
+                                                 table, 64, pool, qcat, T, H, d, r, R), 10)
+        by = T * (H * r * 2 * 2 + D * 2 * 2)
+        print(f"latent_prep T=2048 {tag}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
+        del pool, qcat, olat
+        # ---- decode steps: B sequences of 2,048 cached positions each, one new token each; the pools rotate past L2
+        for B in (8, 64):
+            ctx = 2048
+            ppseq = ctx // 64
+            nrot = max(2, int(300e6 // (B * ppseq * 64 * D * 2)) + 1)
+            pools = [(torch.randn(B * ppseq, 64, D, device=dev) * 0.5).to(torch.bfloat16) for _ in range(nrot)]
+            q1 = (torch.randn(B, H, D, device=dev) * 0.2).to(torch.bfloat16)
+            o1 = torch.empty(B, H, R, device=dev, dtype=torch.bfloat16)
+            tb = ints([[b * ppseq + j for j in range(ppseq)] for b in range(B)])
+            cu1, pos1, sot1 = ints(list(range(B + 1))), ints([ctx - 1] * B), ints(list(range(B)))
+            S = FL.mma_splits(B, B, H, R, r, win, ctx)
+            po = torch.empty(B * H, S, R, device=dev)
+            pml = torch.empty(B * H, S, 2, device=dev)
+            us = _time_graph(lambda i: FL.latent_attention_mma(q1, pools[i % nrot], o1, cu1, pos1, sot1, tb, 64, B, B, H, R, r, 0.1,
+                                                               win, S, po, pml))
+            by = B * min(ctx, win) * D * 2
+            print(f"latent_attention_mma decode B={B:3d} splits={S:2d} {tag}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
+            del pools
+            torch.cuda.empty_cache()
+        # ---- feed-forward kernels
+        F = 4 * W
+        z = (torch.randn(2048, F, device=dev)).to(torch.bfloat16)
+        us = _time_graph(lambda i: K.xielu(z, z, 0.7, 1.1, 0.5), 10)
+        by = z.numel() * 4
+        print(f"xielu 2048 x {F}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
+        E, top, Fe = 16, 2, W // 2
+        nrot = max(2, int(300e6 // (E * 3 * Fe * W * 2)) + 1)
+        gus = [(torch.randn(E, 2, Fe, W, device=dev) * 0.02).to(torch.bfloat16) for _ in range(nrot)]
+        dns = [(torch.randn(E, W, Fe, device=dev) * 0.02).to(torch.bfloat16) for _ in range(nrot)]
+        for B in (8, 64):
+            h = torch.randn(B, W, device=dev).to(torch.bfloat16)
+            idx = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(B)]).to(torch.int32)
+            wts = torch.rand(B, top, device=dev)
+            y = torch.empty(B * top, Fe, device=dev)
+            res = torch.zeros(B, W, device=dev)
+            used = len(set(idx.flatten().tolist()))
+            us = _time_graph(lambda i: K.moe_gate_up(h, gus[i % nrot], idx, wts, y, B, top, True, 7.0, 1.702, 0.5))
+            by = used * 2 * Fe * W * 2
+            print(f"moe_gate_up B={B:3d} E={E} top={top} F={Fe} W={W}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth ({used} experts touched)", flush=True)
+            us = _time_graph(lambda i: K.moe_down(y, dns[i % nrot], idx, res, B, top, None))
+            by = used * Fe * W * 2
+            print(f"moe_down    B={B:3d} E={E} top={top} F={Fe} W={W}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
+        del gus, dns
+        torch.cuda.empty_cache()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample"])
+    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
     a = ap.parse_args()
     ms = [int(x) for x in a.m.split(",")]
+    if a.what == "latent":
+        latent()
+        return
     if a.what == "attn":
         for c in a.ctx.split(","):
             attn(ms, ctx_len=int(c), cluster=not a.scratch)

@@ -279,6 +279,18 @@ def test_latent_attention_kernels_agree_on_made_up_queries():
                                          B, B, H, R, r, scale, window)
         assert rel_err(out2[0::2], want) < 8e-3
         assert torch.equal(out2[1::2].float().cpu(), torch.zeros(T, H, R))
+        # the cached positions cut into shares whose partial results a second kernel merges (steps of few CTAs);
+        # more shares than tiles leaves some of them empty
+        for splits in (2, 5, 32):
+            for (qq, cuq, posq, sotq, tabq, nseq, ntok, pick) in ((q_b, cu, positions, sot, table, 1, T, slice(None)),
+                                                                  (q2, cu2, pos2, sot2, table2, B, B, slice(0, None, 2))):
+                outs = torch.full((ntok, H, R), float("nan"), dtype=torch.bfloat16, device=dev)
+                part_o = torch.full((ntok * H, splits, R), float("nan"), device=dev)
+                part_ml = torch.full((ntok * H, splits, 2), float("nan"), device=dev)
+                fast_latent.latent_attention_mma(qq.to(dev), pool_b.to(dev), outs, cuq, posq, sotq, tabq, page_rows,
+                                                 nseq, ntok, H, R, r, scale, window, splits, part_o, part_ml)
+                assert rel_err(outs[pick], want) < 8e-3, (H, R, r, window, splits)
+    assert fast_latent.mma_splits(8, 8, 16, 128, 32, 1024, 4096) > 1 and fast_latent.mma_splits(1, 4096, 16, 128, 32, 1024, 4096) == 1
 
 
 def test_per_head_products_on_the_tensor_cores_equal_the_plain_ones():
@@ -309,6 +321,12 @@ def test_xielu_router_and_experts_alone():
     out = torch.empty_like(z)
     K.xielu(z, out, float(plain.softplus(p.double())), float(0.5 + plain.softplus(q.double())), 0.6)
     assert rel_err(out, 0.6 * plain.xielu(z.double().cpu(), p, q)) < 1e-6
+    zb = (torch.randn(5, 64, generator=torch.Generator().manual_seed(1)) * 3).to(torch.bfloat16)
+    for n in (64, 63):            # eight elements per thread, and the element-wise form
+        ob = torch.empty(5, n, dtype=torch.bfloat16, device=dev)
+        K.xielu(zb[:, :n].contiguous().to(dev), ob, 0.9, 0.7, 0.6)
+        wantb = 0.6 * plain.xielu(zb[:, :n].double(), torch.log(torch.expm1(torch.tensor(0.9))), torch.log(torch.expm1(torch.tensor(0.2))))
+        assert rel_err(ob, wantb) < 5e-3
     # router: rows with ties (the lower index wins), top 3 of 7
     logits = torch.tensor([[0.1, 2.0, 2.0, -1.0, 2.0, 0.3, 0.2], [5.0, -5.0, 0.0, 0.0, 1.0, 1.0, 1.0]], device=dev)
     idx = torch.empty(2, 3, dtype=torch.int32, device=dev)
