@@ -132,7 +132,7 @@ GG_API gg_moe_gate_up(const void* h, int h_dtype, const void* w_gu, int w_dtype,
 }
 
 // ----------------------------------------------------------------------------- down through the index
-// grid (tokens, ceil(W / 8)); one warp per output element of the token; y[t, k] in shared memory.
+// grid (tokens, ceil(W / 8)); one warp per output element of the token; y[t, k] in shared memory, k by k.
 // w_d [E][W][F].
 template <typename TY, typename TW>
 __global__ void __launch_bounds__(256) moe_down_kernel(const TY* y, const TW* __restrict__ w_d, const int* idx,
@@ -144,28 +144,30 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const TY* y, const TW* __
     const int t = blockIdx.x;
     if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
     const TY* yt = y + (size_t)t * top * F;
-    for (int i = threadIdx.x; i < top * F; i += blockDim.x) ys[i] = to_f<TY>(yt[i]);
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.y * 8 + warp;
-    if (n >= W) return;
     float total = 0.f;
-    for (int k = 0; k < top; ++k) {
-        const int e = idx[(size_t)t * top + k];
-        const TW* wr = w_d + ((size_t)e * W + n) * F;
-        float s = 0.f;
-        for (int i = lane; i < F; i += 32) s = fmaf(to_f<TW>(wr[i]), ys[k * F + i], s);
-        total += warp_sum(s);
+    for (int k = 0; k < top; ++k) {                      // one choice's row at a time in shared memory
+        __syncthreads();
+        for (int i = threadIdx.x; i < F; i += blockDim.x) ys[i] = to_f<TY>(yt[(size_t)k * F + i]);
+        __syncthreads();
+        if (n < W) {
+            const int e = idx[(size_t)t * top + k];
+            const TW* wr = w_d + ((size_t)e * W + n) * F;
+            float s = 0.f;
+            for (int i = lane; i < F; i += 32) s = fmaf(to_f<TW>(wr[i]), ys[i], s);
+            total += warp_sum(s);
+        }
     }
-    if (lane == 0) residual[(size_t)t * W + n] += total;
+    if (n < W && lane == 0) residual[(size_t)t * W + n] += total;
 }
 
 GG_API gg_moe_down(const void* y, int y_dtype, const void* w_d, int w_dtype, const int* idx, float* residual, int T,
                    int W, int F, int top, const int* seq_of_token, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (W <= 0 || F <= 0 || top <= 0 || (size_t)top * F * 4 > 48 * 1024 || (W + 7) / 8 > 65535) return GG_ERR_ARG;
+    if (W <= 0 || F <= 0 || top <= 0 || (size_t)F * 4 > 48 * 1024 || (W + 7) / 8 > 65535) return GG_ERR_ARG;
     dim3 grid(T, (W + 7) / 8);
-    const size_t smem = (size_t)top * F * sizeof(float);
+    const size_t smem = (size_t)F * sizeof(float);
 #define GG_DN(TY, TW) gg_launch(moe_down_kernel<TY, TW>, dim3(grid), dim3(256), smem, stream, 1, (const TY*)y, \
         (const TW*)w_d, idx, residual, W, F, top, seq_of_token)
     if (y_dtype == GG_F32 && w_dtype == GG_F32) GG_DN(float, float);

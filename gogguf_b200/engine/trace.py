@@ -31,6 +31,9 @@ from .model import Model
 from .step import StepEntry, Stepper
 
 
+from ..cache.sequence_cache import PAGE_SIZE
+
+
 class TraceError(ValueError):
     pass
 
@@ -38,7 +41,10 @@ class TraceError(ValueError):
 class TraceRunner:
     def __init__(self, model: Model, max_tokens: int, out_dir: str, graphs: bool = True, layers: bool = False):
         self.model = model
-        self.cache = model.new_cache(max_tokens)
+        # `max_tokens` counts tokens, a sequence holds whole pages: a quarter more pages than the count alone asks
+        # for leaves room for the live requests' partly filled last pages
+        pages = -(-max_tokens // PAGE_SIZE)
+        self.cache = model.new_cache((pages + pages // 4) * PAGE_SIZE)
         if graphs and model.rt.device.type == "cuda":
             from .graphs import GraphStepper
             self.stepper: Stepper = GraphStepper(model, self.cache)
@@ -110,7 +116,7 @@ def main(argv: Optional[list] = None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time (the cache holds a quarter more pages of 64)")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--graphs", dest="graphs", action="store_true", default=True,
                     help="replay plain decode steps as captured CUDA graphs, as generation does (default)")

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import plain_gigopel as plain
-from gigopel_cases import CASES, make_folder, plain_logits
+from gigopel_cases import CASES, dense, layer, make_folder, mixer, moe, plain_logits
 from helpers import random_tokens, read_folder, rel_err
 
 pytestmark = pytest.mark.gpu
@@ -404,3 +404,69 @@ def test_greedy_generation_through_the_entry_point(tmp_path_factory):
         assert [r.tokens for r in again] == [r.tokens for r in out]
         ctx.cache.check()
         assert ctx.cache.live_slots == 0
+
+
+def draw_case(seed: int) -> dict:
+    """A configuration nobody chose: every size, the order of the layers, windows and constants from a seeded generator."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([8, 16, 24]) * r.choice([3, 5, 7, 9])
+    layers = []
+    shapes = []
+    for _ in range(r.choice([1, 2, 3])):                       # a few mixer shapes that layers share or not
+        rot_dim = r.choice([2, 8, 16, 32, 48])
+        shapes.append(mixer(r.choice([1, 2, 3, 5, 8]), r.choice([4, 8, 16, 24, 40, 64]), rot_dim,
+                            r.choice([4, 8, 16, 24, 56]), r.choice([8, 16, 32, 48, 80, 100, 144]),
+                            r.choice([0.05, 0.125, 0.3]), r.choice([100.0, 1e4, 250000.0]),
+                            dims=r.choice([d for d in (2, 4, 8, 16, 32, 48) if d <= rot_dim]),
+                            window=r.choice([None, 1, 2, 17, 63, 64, 65, 128, 200])))
+    for _ in range(r.choice([1, 2, 3, 4, 5])):
+        kind = r.choice(["none", "dense", "moe", "moe"])
+        experts = r.choice([1, 2, 4, 7, 13])
+        mlp = None if kind == "none" else dense(r.choice([8, 24, 40, 72, 200])) if kind == "dense" else \
+            moe(r.choice([8, 16, 40, 96]), r.choice([0.5, 1.0, 4.0]), experts, r.randint(1, min(experts, 4)))
+        layers.append(layer(r.choice(shapes), mlp))
+    return dict(architecture="Gigopel", vocab=r.choice([53, 211, 640, 1031]), width=width,
+                residual_mult=r.choice([0.2, 0.5, 1.0, 1.3]), norm=dict(eps=r.choice([1e-6, 1e-5, 3e-4])), layers=layers)
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_a_configuration_nobody_chose(tmp_path, seed):
+    """Whole, then a prompt and its tail one by one through captured graphs beside a second, shorter request."""
+    import json
+    import os
+    from gogguf_b200.config import config_from_dict
+    from gogguf_b200.engine import StepEntry
+    from gogguf_b200.engine.model import write_random_model
+    cfg = draw_case(seed)
+    n = 150
+    tokens = random_tokens(cfg["vocab"], n, seed)
+    for dtype in ("float32", "bfloat16"):
+        folder = os.path.join(str(tmp_path), dtype)
+        write_random_model(config_from_dict(cfg), seed, folder, dtype=dtype, std=0.12, norm_std=0.1)
+        c, w = read_folder(folder)
+        want = plain_logits(c, w, tokens)
+        model, cache, st = load(folder, dtype, max_tokens=1024)
+        got = run_cut(st, cache, tokens, [n])
+        assert close(got, want, dtype), (json.dumps(cfg), dtype, rel_err(got, want))
+        _, cache_g, gs = load(folder, dtype, max_tokens=1024, graphs=True)
+        a, b = cache_g.open(), cache_g.open()
+        cut = n - 40
+        rows, refs = [], []
+        out = gs.step([StepEntry(a, tokens[:cut], want=[cut - 1]), StepEntry(b, tokens[:9], want=[8])]).clone()
+        rows += [out[0], out[1]]
+        refs += [want[cut - 1], want[8]]
+        for k in range(cut, n):
+            ents = [StepEntry(a, [tokens[k]], want=[0])]
+            if 9 + k - cut < 30:
+                ents.append(StepEntry(b, [tokens[9 + k - cut]], want=[0]))
+            out = gs.step(ents).clone()
+            rows.append(out[0])
+            refs.append(want[k])
+            if len(ents) == 2:
+                rows.append(out[1])
+                refs.append(want[9 + k - cut])
+        cache_g.close(a)
+        cache_g.close(b)
+        cache_g.check()
+        assert close(torch.stack(rows), torch.stack(refs), dtype), (json.dumps(cfg), dtype)
