@@ -244,6 +244,42 @@ def moe_down(y: torch.Tensor, w_d: torch.Tensor, idx: torch.Tensor, residual: to
                                   n_tokens, W, F, int(top), _p(seq_of_token), _stream())
 
 
+def moe_gather(h: torch.Tensor, wts: torch.Tensor, place: Optional[torch.Tensor], xs: torch.Tensor, n_pairs: int,
+               top: int, weight_on_input: bool) -> None:
+    """xs[place[p]] (xs[p] without `place`) = bfloat16(h[p // top] * (wts[p] if the weight sits on the input))."""
+    _need(h, torch.bfloat16, "h")
+    _need(xs, torch.bfloat16, "xs")
+    kernel("moe", "gg_moe_gather")(_p(h), _p(wts), _p(place), _p(xs), int(n_pairs), h.shape[-1], int(top),
+                                    int(weight_on_input), _stream())
+
+
+def moe_combine(rows: torch.Tensor, place: Optional[torch.Tensor], residual: torch.Tensor, n_tokens: int, top: int,
+                seq_of_token: Optional[torch.Tensor]) -> None:
+    """residual[t] += sum over k (in order) of rows[place[t * top + k]], or of rows[t * top + k] without `place`."""
+    _need(rows, torch.float32, "rows")
+    _need(residual, torch.float32, "residual")
+    kernel("moe", "gg_moe_combine")(_p(rows), _p(place), _p(residual), int(n_tokens), residual.shape[-1], int(top),
+                                     _p(seq_of_token), _stream())
+
+
+MOE_MMA_MAX_PAIRS = 2048      # the most (token, choice) pairs the mma.sync experts kernel takes (csrc/moe.cu)
+
+
+def moe_expert_mma(x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor, n_pairs: int, out: torch.Tensor, gated: bool,
+                   limit: float = 0.0, slope: float = 1.0, out_scale: float = 1.0,
+                   wts: Optional[torch.Tensor] = None) -> None:
+    """The experts' products on the tensor cores for up to 2,048 pairs, through the chosen index.  gated: x [P, K]
+    against w [E, 2, N, K], out bfloat16 [P, N] = out_scale * act(gate, up) (* wts[p]); else w [E, N, K], out float32."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.bfloat16 if gated else torch.float32, "out")
+    E, N, K = w.shape[0], w.shape[-2], w.shape[-1]
+    if x.shape[-1] != K or out.shape[-1] != N or (gated and (w.dim() != 4 or w.shape[1] != 2)):
+        raise KernelError("moe_expert_mma: shapes disagree")
+    kernel("moe", "gg_moe_expert_mma")(_p(x), _p(w), _p(idx), int(n_pairs), E, _p(out), N, K, int(gated), float(limit),
+                                        float(slope), float(out_scale), _p(wts), _stream())
+
+
 def wait_probe(limit_cycles: int, code: int, status: torch.Tensor) -> torch.Tensor:
     """Run the package's bounded wait on a barrier nothing arrives at (csrc/diagnostics.cu) and return the
     kernel's report (5 int32 on the device): both roles' return values, their elapsed cycles / 1024, the

@@ -243,6 +243,13 @@ def latent(sizes=((16, 64, 32, 64, 256, 1024, 2048), (32, 128, 64, 128, 512, 204
             us = _time_graph(lambda i: K.moe_gate_up(h, gus[i % nrot], idx, wts, y, B, top, True, 7.0, 1.702, 0.5))
             by = used * 2 * Fe * W * 2
             print(f"moe_gate_up B={B:3d} E={E} top={top} F={Fe} W={W}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth ({used} experts touched)", flush=True)
+            xs = h.repeat_interleave(top, 0).contiguous()
+            yb = torch.empty(B * top, Fe, device=dev, dtype=torch.bfloat16)
+            rows = torch.empty(B * top, W, device=dev)
+            us2 = _time_graph(lambda i: K.moe_expert_mma(xs, gus[i % nrot], idx, B * top, yb, True, 7.0, 1.702, 0.5))
+            print(f"moe_expert_mma gate/up B={B:3d}: {us2:9.1f} us {by / us2 / 1e3:7.1f} GB/s {by / us2 / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
+            us2 = _time_graph(lambda i: K.moe_expert_mma(yb, dns[i % nrot], idx, B * top, rows, False))
+            print(f"moe_expert_mma down    B={B:3d}: {us2:9.1f} us {by / 2 / us2 / 1e3:7.1f} GB/s {by / 2 / us2 / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
             us = _time_graph(lambda i: K.moe_down(y, dns[i % nrot], idx, res, B, top, None))
             by = used * Fe * W * 2
             print(f"moe_down    B={B:3d} E={E} top={top} F={Fe} W={W}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)

@@ -210,7 +210,7 @@ GG_API gg_moe_sort(const int* idx, int P, int E, int* offsets, int* place, int* 
     return gg_last_error();
 }
 
-// xs[place[p]] = bfloat16(h[p / top] * (weight_on_input ? wts[p] : 1)); one block per pair.
+// xs[place[p]] (xs[p] without `place`) = bfloat16(h[p / top] * (weight_on_input ? wts[p] : 1)); one block per pair.
 __global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* h, const float* wts, const int* place, bf16* xs,
                                                          int W, int top, int weight_on_input) {
     pdl_launch();
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* h, const fl
     const int p = blockIdx.x;
     const float f = weight_on_input ? wts[p] : 1.0f;
     const bf16* src = h + (size_t)(p / top) * W;
-    bf16* dst = xs + (size_t)place[p] * W;
+    bf16* dst = xs + (size_t)(place != nullptr ? place[p] : p) * W;
     for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = __float2bfloat16_rn(__bfloat162float(src[i]) * f);
 }
 
@@ -268,7 +268,7 @@ GG_API gg_moe_invert(const int* place, int* pair_of, int P, cudaStream_t stream)
     return gg_last_error();
 }
 
-// residual[t, :] += sum_k rows[place[t * top + k], :]
+// residual[t, :] += sum_k rows[place[t * top + k], :]  (without `place`: the rows are in pair order)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* rows, const int* place, float* residual, int W,
                                                           int top, const int* __restrict__ seq_of_token) {
     pdl_launch();
@@ -277,7 +277,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* rows, con
     if (seq_of_token != nullptr && seq_of_token[t] < 0) return;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s += rows[(size_t)place[(size_t)t * top + k] * W + i];
+        for (int k = 0; k < top; ++k) {
+            const size_t p = (size_t)t * top + k;
+            s += rows[(place != nullptr ? (size_t)place[p] : p) * W + i];
+        }
         residual[(size_t)t * W + i] += s;
     }
 }
@@ -287,4 +290,167 @@ GG_API gg_moe_combine(const float* rows, const int* place, float* residual, int 
     if (T <= 0) return 0;
     gg_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, 1, rows, place, residual, W, top, seq_of_token);
     return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- the experts on mma.sync (few pairs)
+// Decode steps and short prompts in bfloat16: a CTA belongs to one expert and 64 of its output rows (features of
+// gate and up, or elements of the down projection).  It collects the pairs that chose its expert (none: it leaves
+// without touching a weight), takes their input rows as the 16-row operand of m16n8k16 and streams its weight rows
+// once, 64 columns of k at a time through two cp.async stages.  x [P, K] in pair order (gate/up: the token's row
+// times the weight where the weight sits on the input; down: the activation rows).  GATED: w [E][2][N][K], out[p, n] =
+// out_scale * act(gate, up) (* wts[p] where given) as bfloat16; else w [E][N][K] and out[p, n] the float32 sum.
+__device__ __forceinline__ void mx_mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mx_cp16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void mx_ldsm(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+#define MX_KS 64
+#define MX_LD (MX_KS + 8)
+#define MX_MAXP 2048
+
+template <bool GATED>
+__global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, const bf16* __restrict__ w, const int* idx, int P,
+                                                             void* out, int N, int K, float limit, float slope,
+                                                             float out_scale, const float* wts) {
+    pdl_launch();
+    extern __shared__ __align__(16) unsigned char mx_raw[];
+    constexpr int TILES = GATED ? 3 : 2;                 // x, gate (or the one matrix), up
+    bf16* stage0 = reinterpret_cast<bf16*>(mx_raw);      // [2 stages][TILES][64][MX_LD]
+    int* list = reinterpret_cast<int*>(mx_raw + (size_t)2 * TILES * 64 * MX_LD * sizeof(bf16));
+    __shared__ int count;
+    const int e = blockIdx.x, n0 = blockIdx.y * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) count = 0;
+    __syncthreads();
+    pdl_wait();
+    for (int p = tid; p < P; p += 128)
+        if (idx[p] == e) list[atomicAdd(&count, 1)] = p;
+    __syncthreads();
+    const int cnt = count;
+    if (cnt == 0) return;
+    const bf16* wg = w + ((size_t)e * (GATED ? 2 : 1) * N + n0) * K;
+    const bf16* wu = wg + (size_t)N * K;
+    const int ksteps = (K + MX_KS - 1) / MX_KS;
+    const int g = lane >> 2, q4 = lane & 3;
+    for (int m0 = 0; m0 < cnt; m0 += 64) {
+        const int rows = min(64, cnt - m0);
+        auto load = [&](int kc, int st) {
+            bf16* xs = stage0 + (size_t)st * TILES * 64 * MX_LD;
+            bf16* gs = xs + 64 * MX_LD;
+            bf16* us = gs + 64 * MX_LD;
+            const int k0 = kc * MX_KS;
+            for (int c = tid; c < 64 * (MX_KS / 8); c += 128) {
+                const int row = c / (MX_KS / 8), kk = (c % (MX_KS / 8)) * 8;
+                const bool kin = k0 + kk < K;
+                bf16* dx = xs + row * MX_LD + kk;
+                if (row < rows && kin) mx_cp16(dx, x + (size_t)list[m0 + row] * K + k0 + kk);
+                else *reinterpret_cast<uint4*>(dx) = make_uint4(0u, 0u, 0u, 0u);
+                bf16* dg = gs + row * MX_LD + kk;
+                if (n0 + row < N && kin) mx_cp16(dg, wg + (size_t)row * K + k0 + kk);
+                else *reinterpret_cast<uint4*>(dg) = make_uint4(0u, 0u, 0u, 0u);
+                if (GATED) {
+                    bf16* du = us + row * MX_LD + kk;
+                    if (n0 + row < N && kin) mx_cp16(du, wu + (size_t)row * K + k0 + kk);
+                    else *reinterpret_cast<uint4*>(du) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        float ag[8][4], au[GATED ? 8 : 1][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { ag[i][j] = 0.f; if (GATED) au[i][j] = 0.f; }
+        load(0, 0);
+        for (int kc = 0; kc < ksteps; ++kc) {
+            if (kc + 1 < ksteps) {
+                load(kc + 1, (kc + 1) & 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            if (warp * 16 < rows) {                      // warps without pairs only copy
+                const bf16* xs = stage0 + (size_t)(kc & 1) * TILES * 64 * MX_LD;
+                const bf16* gs = xs + 64 * MX_LD;
+                const bf16* us = gs + 64 * MX_LD;
+#pragma unroll
+                for (int ks = 0; ks < MX_KS / 16; ++ks) {
+                    uint32_t a[4];
+                    mx_ldsm(a, xs + (warp * 16 + (lane & 15)) * MX_LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        const int off = (np * 16 + (lane & 7) + (lane >> 4) * 8) * MX_LD + ks * 16 + ((lane >> 3) & 1) * 8;
+                        uint32_t b[4];
+                        mx_ldsm(b, gs + off);
+                        mx_mma16816(ag[2 * np], a, b[0], b[1]);
+                        mx_mma16816(ag[2 * np + 1], a, b[2], b[3]);
+                        if (GATED) {
+                            mx_ldsm(b, us + off);
+                            mx_mma16816(au[2 * np], a, b[0], b[1]);
+                            mx_mma16816(au[2 * np + 1], a, b[2], b[3]);
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = warp * 16 + g + half * 8;
+            if (row >= rows) continue;
+            const int p = list[m0 + row];
+            const float f = GATED ? out_scale * (wts != nullptr ? wts[p] : 1.0f) : 1.0f;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int n = n0 + nt * 8 + 2 * q4 + j;
+                    if (n >= N) continue;
+                    if (GATED)
+                        reinterpret_cast<bf16*>(out)[(size_t)p * N + n] =
+                            __float2bfloat16_rn(clamped_glu(ag[nt][2 * half + j], au[nt][2 * half + j], limit, slope) * f);
+                    else
+                        reinterpret_cast<float*>(out)[(size_t)p * N + n] = ag[nt][2 * half + j];
+                }
+        }
+        __syncthreads();
+    }
+}
+
+// gated != 0: x [P, K], w [E, 2, N, K], out bfloat16 [P, N]; else w [E, N, K], out float32 [P, N].  P <= 2,048 pairs.
+GG_API gg_moe_expert_mma(const void* x, const void* w, const int* idx, int P, int E, void* out, int N, int K, int gated,
+                         float limit, float slope, float out_scale, const float* wts, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (E <= 0 || N <= 0 || K <= 0 || (K % 8) || P > MX_MAXP || (N + 63) / 64 > 65535 ||
+        (((uintptr_t)x | (uintptr_t)w) & 15))
+        return GG_ERR_ARG;
+    dim3 grid(E, (N + 63) / 64);
+    const size_t smem = (size_t)2 * (gated ? 3 : 2) * 64 * MX_LD * sizeof(bf16) + MX_MAXP * sizeof(int);
+    static bool set_g = false, set_p = false;
+    if (gated) {
+        if (!set_g) {
+            cudaError_t er = cudaFuncSetAttribute(moe_expert_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (er != cudaSuccess) return (int)er;
+            set_g = true;
+        }
+        return gg_launch(moe_expert_mma_kernel<true>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)x, (const bf16*)w, idx, P,
+                         out, N, K, limit, slope, out_scale, wts);
+    }
+    if (!set_p) {
+        cudaError_t er = cudaFuncSetAttribute(moe_expert_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (er != cudaSuccess) return (int)er;
+        set_p = true;
+    }
+    return gg_launch(moe_expert_mma_kernel<false>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)x, (const bf16*)w, idx, P,
+                     out, N, K, limit, slope, out_scale, wts);
 }

@@ -7,9 +7,10 @@ Routed experts (`routed_experts`): router logits W_r h in float32, scores by sig
 largest chosen, weights the chosen scores (optionally renormalised), the weight applied to the expert's input
 or to its output.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
 act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
-Steps of few tokens (and the 32-bit path) reach the experts' matrices through the chosen index, token by
-token, with nothing read back; steps of many tokens in bfloat16 sort the (token, choice) pairs by expert and run
-one tensor-core product per expert on its rows.
+The experts' matrices are reached through the chosen index with nothing read back: on the CUDA cores pair by pair
+(the 32-bit path, sizes the tensor-core forms do not take), or in bfloat16 on mma.sync, a CTA per expert and 64
+output rows with the expert's pairs as the operand (decode steps, short prompts).  Steps of many tokens in
+bfloat16 sort the (token, choice) pairs by expert and run one tcgen05 product per expert on its rows.
 """
 from __future__ import annotations
 
@@ -123,6 +124,9 @@ class RoutedExperts:
         self.w_d = torch.stack(dn, dim=0).contiguous()        # [E, W, F]
         self.out_scale = 1.0
         self._grouped = None
+        # rows on 16-byte boundaries: what the tensor-core forms (mma.sync for few pairs, tcgen05 for many) take
+        self._mma = (rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16
+                     and self.hidden % 8 == 0 and self.inter % 8 == 0)
         if rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16:
             from . import experts_grouped
             self._grouped = experts_grouped.try_make(self)
@@ -146,6 +150,18 @@ class RoutedExperts:
         idx, wts = self.route(h, ctx)
         if self._grouped is not None and self._grouped.takes(ctx):
             self._grouped.run(h, idx, wts, residual, ctx)
+            return
+        P = T * self.top
+        if self._mma and P <= K.MOE_MMA_MAX_PAIRS and h.dtype == torch.bfloat16:
+            # few pairs in bfloat16: the experts' rows stream once through mma.sync, the pairs' rows as the operand
+            xs = ctx.ws.get("moe_rows_in", (P, self.hidden), torch.bfloat16)
+            K.moe_gather(h, wts, None, xs, P, self.top, self.on_input)
+            yb = ctx.ws.get("moe_act_rows", (P, self.inter), torch.bfloat16)
+            K.moe_expert_mma(xs, self.w_gu, idx, P, yb, True, self.limit, self.slope, self.out_scale,
+                             None if self.on_input else wts)
+            rows = ctx.ws.get("moe_rows_out", (P, self.hidden), torch.float32)
+            K.moe_expert_mma(yb, self.w_d, idx, P, rows, False)
+            K.moe_combine(rows, None, residual, T, self.top, ctx.seq_of_token)
             return
         y = ctx.ws.get("moe_act", (T * self.top, self.inter), torch.float32)
         K.moe_gate_up(h, self.w_gu, idx, wts, y, T, self.top, self.on_input, self.limit, self.slope, self.out_scale)

@@ -357,6 +357,32 @@ def test_xielu_router_and_experts_alone():
     K.moe_gate_up(h.to(dev), w_gu, ch.to(dev), wt.to(dev), y, T, top, True, limit, 1.702, 0.3)
     K.moe_down(y, w_d, ch.to(dev), res, T, top, None)
     assert rel_err(res, want) < 1e-5
+    # the same on mma.sync in bfloat16: pairs collected per expert, weight on the input and on the output
+    for T2, top2 in ((9, 2), (1, 1), (200, 3)):
+        h2 = torch.randn(T2, W, generator=g)
+        ch2 = torch.stack([torch.randperm(E, generator=g)[:top2] for _ in range(T2)]).to(torch.int32)
+        wt2 = torch.rand(T2, top2, generator=g) + 0.2
+        P2 = T2 * top2
+        for on_input in (True, False):
+            want2 = torch.zeros(T2, W, dtype=torch.float64)
+            hb = h2.to(torch.bfloat16)
+            tb = {k: v.to(torch.bfloat16).double() for k, v in t.items()}
+            for i in range(T2):
+                for k in range(top2):
+                    e = int(ch2[i, k])
+                    xin = (wt2[i, k] * hb[i].float()).to(torch.bfloat16).double() if on_input else hb[i].double()
+                    o = plain.expert(xin[None], tb, f"e{e}.", limit)[0]
+                    want2[i] += 0.3 * o * (1.0 if on_input else float(wt2[i, k]))
+            xs = torch.empty(P2, W, dtype=torch.bfloat16, device=dev)
+            K.moe_gather(hb.to(dev), wt2.to(dev), None, xs, P2, top2, on_input)
+            yb = torch.full((P2, F), float("nan"), dtype=torch.bfloat16, device=dev)
+            K.moe_expert_mma(xs, w_gu.to(torch.bfloat16), ch2.to(dev), P2, yb, True, limit, 1.702, 0.3,
+                             None if on_input else wt2.to(dev))
+            rows2 = torch.full((P2, W), float("nan"), device=dev)
+            K.moe_expert_mma(yb, w_d.to(torch.bfloat16), ch2.to(dev), P2, rows2, False)
+            res2 = torch.zeros(T2, W, device=dev)
+            K.moe_combine(rows2, None, res2, T2, top2, None)
+            assert rel_err(res2, want2) < 1e-2, (T2, top2, on_input)
     assert float((torch.einsum("tw,efw->tef", h, torch.stack([t[f"e{e}.gate"] for e in range(E)])).abs() > limit)
                  .float().mean()) > 0.05          # the clamp is in play
 
