@@ -212,6 +212,16 @@ def latent_attention_plain(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Te
 
 
 # ------------------------------------------------------------------------------- routed experts
+def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_tokens: int) -> None:
+    """z[t, e] = wr[e] . h[t], float32 sums on the CUDA cores (the router is never computed in reduced precision)."""
+    _need(z, torch.float32, "router logits")
+    E, W = wr.shape
+    if h.shape[-1] != W or z.shape[-1] != E or not h.is_contiguous() or not wr.is_contiguous():
+        raise KernelError("moe_router_logits: shapes disagree")
+    kernel("moe", "gg_moe_router_logits")(_p(h), dtype_code(h.dtype), _p(wr), dtype_code(wr.dtype), _p(z), int(n_tokens),
+                                           W, E, _stream())
+
+
 def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, seq_of_token: Optional[torch.Tensor],
               softmax: bool = False, renormalize: bool = False, rows: Optional[int] = None) -> None:
     _need(z, torch.float32, "router logits")
@@ -262,13 +272,13 @@ def moe_combine(rows: torch.Tensor, place: Optional[torch.Tensor], residual: tor
                                      _p(seq_of_token), _stream())
 
 
-MOE_MMA_MAX_PAIRS = 2048      # the most (token, choice) pairs the mma.sync experts kernel takes (csrc/moe.cu)
+MOE_MMA_MAX_PAIRS = 8192      # the most (token, choice) pairs the mma.sync experts kernel takes (csrc/moe.cu)
 
 
 def moe_expert_mma(x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor, n_pairs: int, out: torch.Tensor, gated: bool,
                    limit: float = 0.0, slope: float = 1.0, out_scale: float = 1.0,
                    wts: Optional[torch.Tensor] = None) -> None:
-    """The experts' products on the tensor cores for up to 2,048 pairs, through the chosen index.  gated: x [P, K]
+    """The experts' products on the tensor cores for up to 8,192 pairs, through the chosen index.  gated: x [P, K]
     against w [E, 2, N, K], out bfloat16 [P, N] = out_scale * act(gate, up) (* wts[p]); else w [E, N, K], out float32."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")

@@ -12,6 +12,45 @@
 // Router scores, the choice, the weights and all sums are float32.
 #include "common.cuh"
 
+// ----------------------------------------------------------------------------- router logits
+// z[t, e] = Wr[e] . h[t] in float32: a warp per (token, expert), the token's row in shared memory.  A product of so
+// few output columns would be one or two CTAs of the tiled kernels; this one has a CTA per token and 8 experts.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(const TX* h, const TW* __restrict__ wr, float* z, int W, int E) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float rx[];
+    const int t = blockIdx.x;
+    const TX* ht = h + (size_t)t * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) rx[i] = to_f<TX>(ht[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * 8 + warp;
+    if (e >= E) return;
+    const TW* w = wr + (size_t)e * W;
+    float s = 0.f;
+    for (int i = lane; i < W; i += 32) s = fmaf(to_f<TW>(w[i]), rx[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[(size_t)t * E + e] = s;
+}
+
+GG_API gg_moe_router_logits(const void* h, int h_dtype, const void* wr, int w_dtype, float* z, int T, int W, int E,
+                            cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (W <= 0 || E <= 0 || (size_t)W * 4 > 48 * 1024 || (E + 7) / 8 > 65535) return GG_ERR_ARG;
+    dim3 grid(T, (E + 7) / 8);
+    const size_t smem = (size_t)W * sizeof(float);
+#define GG_RL(TX, TW) gg_launch(moe_router_logits_kernel<TX, TW>, dim3(grid), dim3(256), smem, stream, 1, (const TX*)h, \
+        (const TW*)wr, z, W, E)
+    if (h_dtype == GG_F32 && w_dtype == GG_F32) GG_RL(float, float);
+    else if (h_dtype == GG_BF16 && w_dtype == GG_BF16) GG_RL(bf16, bf16);
+    else if (h_dtype == GG_BF16 && w_dtype == GG_F32) GG_RL(bf16, float);
+    else if (h_dtype == GG_F32 && w_dtype == GG_BF16) GG_RL(float, bf16);
+    else return GG_ERR_DTYPE;
+#undef GG_RL
+    return gg_last_error();
+}
+
 // ----------------------------------------------------------------------------- route
 // One warp per token.  z [T, E] float32 logits.  softmax != 0: scores are softmax(z), else sigmoid(z).
 __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, int E, int top, int softmax, int renorm,
@@ -315,7 +354,7 @@ __device__ __forceinline__ void mx_ldsm(uint32_t* r, const void* p) {
 }
 #define MX_KS 64
 #define MX_LD (MX_KS + 8)
-#define MX_MAXP 2048
+#define MX_MAXP 8192
 
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, const bf16* __restrict__ w, const int* idx, int P,
@@ -427,7 +466,7 @@ __global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, cons
     }
 }
 
-// gated != 0: x [P, K], w [E, 2, N, K], out bfloat16 [P, N]; else w [E, N, K], out float32 [P, N].  P <= 2,048 pairs.
+// gated != 0: x [P, K], w [E, 2, N, K], out bfloat16 [P, N]; else w [E, N, K], out float32 [P, N].  P <= 8,192 pairs.
 GG_API gg_moe_expert_mma(const void* x, const void* w, const int* idx, int P, int E, void* out, int N, int K, int gated,
                          float limit, float slope, float out_scale, const float* wts, cudaStream_t stream) {
     if (P <= 0) return 0;

@@ -26,6 +26,9 @@ from .base import Linear, Runtime, StepContext
 from .registry import register_feed_forward
 
 
+SORTED_FORM_MIN_WORK = 1.5e9      # rows per expert x inner width x width from which prompts take the sorted form
+
+
 def _softplus(v: float) -> float:
     return math.log1p(math.exp(-abs(v))) + max(v, 0.0)
 
@@ -139,7 +142,7 @@ class RoutedExperts:
     def route(self, h: torch.Tensor, ctx: StepContext):
         T = ctx.n_tokens
         z = ctx.ws.get("moe_logits", (T, self.E), torch.float32)
-        K.gemm_plain(h, self.router_w, z, m=T)           # CUDA cores, float32 sums: the router is never reduced
+        K.moe_router_logits(h, self.router_w, z, T)      # CUDA cores, float32 sums: the router is never reduced
         idx = ctx.ws.get("moe_idx", (T, self.top), torch.int32)
         wts = ctx.ws.get("moe_wts", (T, self.top), torch.float32)
         K.moe_route(z, self.top, idx, wts, ctx.seq_of_token, softmax=self.softmax, renormalize=self.renorm, rows=T)
@@ -148,10 +151,14 @@ class RoutedExperts:
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
         idx, wts = self.route(h, ctx)
-        if self._grouped is not None and self._grouped.takes(ctx):
+        P = T * self.top
+        # the sorted form pays one launch per expert and matrix behind a read-back: worth it where an expert's
+        # product is large (measured: 256 rows of 2,048 x 4,096 yes, of 1,024 x 2,048 no)
+        prefer_mma = (self._mma and P <= K.MOE_MMA_MAX_PAIRS
+                      and (P / self.E) * self.inter * self.hidden < SORTED_FORM_MIN_WORK)
+        if self._grouped is not None and self._grouped.takes(ctx) and not prefer_mma:
             self._grouped.run(h, idx, wts, residual, ctx)
             return
-        P = T * self.top
         if self._mma and P <= K.MOE_MMA_MAX_PAIRS and h.dtype == torch.bfloat16:
             # few pairs in bfloat16: the experts' rows stream once through mma.sync, the pairs' rows as the operand
             xs = ctx.ws.get("moe_rows_in", (P, self.hidden), torch.bfloat16)

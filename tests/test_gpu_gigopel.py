@@ -60,7 +60,7 @@ def test_whole_prompts_and_every_layer(tmp_path_factory, name, dtype):
     folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
     cfg, w = read_folder(folder)
     model, cache, st = load(folder, dtype)
-    for n in (1, 2, 150) + ((600,) if name == "W" else ()):     # 600 tokens: the experts' sorted form in bfloat16
+    for n in (1, 2, 150) + ((600,) if name == "W" else ()):     # 600 tokens: more pairs per expert than one tile holds
         tokens = random_tokens(cfg["vocab"], n, seed=n)
         want_layers = []
         want = plain_logits(cfg, w, tokens, want_layers)
@@ -327,6 +327,13 @@ def test_xielu_router_and_experts_alone():
         K.xielu(zb[:, :n].contiguous().to(dev), ob, 0.9, 0.7, 0.6)
         wantb = 0.6 * plain.xielu(zb[:, :n].double(), torch.log(torch.expm1(torch.tensor(0.9))), torch.log(torch.expm1(torch.tensor(0.2))))
         assert rel_err(ob, wantb) < 5e-3
+    # router logits: float32 sums of a bfloat16 or float32 row against every expert's row
+    gr = torch.Generator().manual_seed(8)
+    for dt in (torch.float32, torch.bfloat16):
+        hr, wrr = torch.randn(5, 72, generator=gr).to(dt), torch.randn(11, 72, generator=gr).to(dt)
+        zr = torch.empty(5, 11, device=dev)
+        K.moe_router_logits(hr.to(dev), wrr.to(dev), zr, 5)
+        assert rel_err(zr, hr.double() @ wrr.double().T) < 1e-6
     # router: rows with ties (the lower index wins), top 3 of 7
     logits = torch.tensor([[0.1, 2.0, 2.0, -1.0, 2.0, 0.3, 0.2], [5.0, -5.0, 0.0, 0.0, 1.0, 1.0, 1.0]], device=dev)
     idx = torch.empty(2, 3, dtype=torch.int32, device=dev)
@@ -387,19 +394,28 @@ def test_xielu_router_and_experts_alone():
                  .float().mean()) > 0.05          # the clamp is in play
 
 
-def test_experts_sorted_form_equals_the_form_through_the_index(tmp_path_factory, monkeypatch):
-    from gogguf_b200.parts import experts_grouped
+def test_the_three_forms_of_the_experts_agree(tmp_path_factory, monkeypatch):
+    """Sorted by expert with one tcgen05 product per expert; through the index on mma.sync; through the index on
+    the CUDA cores: the same prompt through each."""
+    from gogguf_b200.parts import experts, experts_grouped
     folder = make_folder(tmp_path_factory.getbasetemp(), "W", "bfloat16")
     cfg, w = read_folder(folder)
     tokens = random_tokens(cfg["vocab"], 700, seed=4)
     model, cache, st = load(folder, "bfloat16")
-    assert all(b.feed_forward._grouped is not None for b in model.blocks if hasattr(b.feed_forward, "_grouped"))
+    routed = [b.feed_forward for b in model.blocks if hasattr(b.feed_forward, "_grouped")]
+    assert routed and all(p._grouped is not None and p._mma for p in routed)
+    on_mma = run_cut(st, cache, tokens, [700])
+    monkeypatch.setattr(experts, "SORTED_FORM_MIN_WORK", 0.0)          # this small model would not take it by itself
     sorted_form = run_cut(st, cache, tokens, [700])
     monkeypatch.setattr(experts_grouped, "MIN_PAIRS", 1 << 30)
-    through_index = run_cut(st, cache, tokens, [700])
-    assert not torch.equal(sorted_form, through_index)          # two routes
-    assert close(sorted_form, through_index, "bfloat16")
-    assert close(sorted_form, plain_logits(cfg, w, tokens), "bfloat16")
+    for p in routed:
+        p._mma = False
+    on_cuda_cores = run_cut(st, cache, tokens, [700])
+    assert not torch.equal(sorted_form, on_mma) and not torch.equal(on_mma, on_cuda_cores)      # three routes
+    want = plain_logits(cfg, w, tokens)
+    for got in (on_mma, sorted_form, on_cuda_cores):
+        assert close(got, want, "bfloat16")
+    assert close(sorted_form, on_mma, "bfloat16") and close(on_cuda_cores, on_mma, "bfloat16")
 
 
 def test_greedy_generation_through_the_entry_point(tmp_path_factory):
