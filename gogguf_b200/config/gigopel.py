@@ -83,7 +83,9 @@ class LatentAttentionConfig:
             raise ConfigError(f"gigopel config: {where}.rot.base must be > 0")
         return cls(heads=_pos_int(d, "heads", where), dim=_pos_int(d, "dim", where), rot_dim=rot_dim,
                    vdim=_pos_int(d, "vdim", where), kv_rank=_pos_int(d, "kv_rank", where),
-                   scale=_number(d, "scale", where), rot_base=base, rot_dims=dims, window=window)
+                   scale=_number(d, "scale", where) if d.get("scale") is not None
+                   else (_pos_int(d, "dim", where) + rot_dim) ** -0.5,
+                   rot_base=base, rot_dims=dims, window=window)
 
     def to_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = dict(heads=self.heads, dim=self.dim, rot_dim=self.rot_dim, vdim=self.vdim,
@@ -164,7 +166,8 @@ class GigopelConfig:
         eos = d.get("eos_token_id")
         eos_ids = () if eos is None else tuple(int(x) for x in (eos if isinstance(eos, (list, tuple)) else [eos]))
         return cls(vocab=_pos_int(d, "vocab", "config"), width=_pos_int(d, "width", "config"),
-                   residual_mult=_number(d, "residual_mult", "config"), norm_eps=eps, layers=tuple(layers),
+                   residual_mult=_number(d, "residual_mult", "config") if d.get("residual_mult") is not None else 1.0,
+                   norm_eps=eps, layers=tuple(layers),
                    eos_token_ids=eos_ids, initializer_range=float(d.get("initializer_range", 0.05)))
 
     # ------------------------------------------------------------------ write

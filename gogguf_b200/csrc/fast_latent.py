@@ -26,9 +26,11 @@ def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tens
                          positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
                          page_size: int, n_seqs: int, n_tokens: int, heads: int, R: int, r: int, scale: float,
                          window: int, splits: int = 1, part_o: Optional[torch.Tensor] = None,
-                         part_ml: Optional[torch.Tensor] = None) -> None:
+                         part_ml: Optional[torch.Tensor] = None, max_new: Optional[int] = None) -> None:
     """splits > 1 cuts every CTA's range of cached positions into that many shares (steps with few CTAs); part_o
-    float32 [n_tokens * heads, splits, R] and part_ml [n_tokens * heads, splits, 2] take the partial results."""
+    float32 [n_tokens * heads, splits, R] and part_ml [n_tokens * heads, splits, 2] take the partial results.
+    max_new: the most new tokens any sequence brings (default: all could be one sequence's); a step of few rows
+    per sequence keeps less shared memory for its queries."""
     for t in (qcat, pool, out):
         if t.dtype != torch.bfloat16:
             raise KernelError("latent_attention_mma takes bfloat16 queries, cache and output")
@@ -38,7 +40,8 @@ def latent_attention_mma(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Tens
         seq_of_token.data_ptr(), page_table.data_ptr(), page_table.shape[-1], int(page_size), pool.shape[0],
         int(n_seqs), int(n_tokens), heads, R, r, float(scale), int(window), int(splits),
         part_o.data_ptr() if part_o is not None else 0, part_ml.data_ptr() if part_ml is not None else 0,
-        status_word(qcat.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        int(max_new) if max_new is not None else int(n_tokens), status_word(qcat.device).data_ptr(),
+        torch.cuda.current_stream().cuda_stream)
 
 
 def mma_splits(n_seqs: int, n_tokens: int, heads: int, R: int, r: int, window: int, max_ctx: int) -> int:
@@ -68,7 +71,8 @@ class _Fast:
             part_o = ctx.ws.get("lat_part_o", (T * H, splits, R), torch.float32)
             part_ml = ctx.ws.get("lat_part_ml", (T * H, splits, 2), torch.float32)
         latent_attention_mma(qcat, pool, out, ctx.cu_seqlens, ctx.positions, ctx.seq_of_token, table, page_size,
-                             ctx.n_seqs, T, H, R, self.r, self.scale, self.window, splits, part_o, part_ml)
+                             ctx.n_seqs, T, H, R, self.r, self.scale, self.window, splits, part_o, part_ml,
+                             max_new=max(int(ctx.max_new), 1))
 
     def expand(self, olat: torch.Tensor, uv: torch.Tensor, av: torch.Tensor, m: int, alpha: float) -> None:
         """av[t, h, :] = alpha * Wuv_h olat[t, h]."""

@@ -193,7 +193,7 @@ GG_API gg_headwise_gemm(const void* x, int x_dtype, long long ldx, long long hx,
 // One block per (token, head).  The token at position p of sequence b reads the pool rows of positions lo..p,
 // lo = max(0, p - window + 1) for a windowed layer (itself included: its row was written by latent_prep).
 #define LAT_WARPS 4
-#define LAT_MAXR 1024
+#define LAT_MAXR 2048
 
 template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attention_plain_kernel(
@@ -404,12 +404,14 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const bf16* qcat, const bf16* pool, int pool_row, bf16* out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
     int max_pages, int page_size, int n_seqs, int H, int R, int r, float scale_log2, int window, const PageBounds pb,
-    float* part_o, float* part_ml) {
+    float* part_o, float* part_ml, int q_rows) {
     pdl_launch();
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = R + r, LD = D + 8;
-    bf16* qs = reinterpret_cast<bf16*>(smraw);          // [64][LD]
-    bf16* ks = qs + 64 * LD;                            // [2][KT][LD]
+    // q_rows (a multiple of 16, at most 64): the most rows a CTA of this launch can have; a decode step of few
+    // heads keeps less shared memory for queries, so that more CTAs share an SM
+    bf16* qs = reinterpret_cast<bf16*>(smraw);          // [q_rows][LD]
+    bf16* ks = qs + q_rows * LD;                        // [2][KT][LD]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // which sequence and which 64 rows of it
     int b = 0, chunk = blockIdx.x, t0 = 0, n_new = 0;
@@ -467,7 +469,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     };
     {   // the queries of this CTA: rows_here consecutive rows of qcat
         const bf16* qsrc = qcat + ((size_t)t0 * H + f0) * D;
-        for (int row = warp; row < 64; row += 4) {
+        for (int row = warp; row < q_rows; row += 4) {
             bf16* d = qs + row * LD;
             if (row < rows_here) {
                 for (int c = lane; c < chunks_per_row; c += 32) cp_async16(d + c * 8, qsrc + (size_t)row * D + c * 8);
@@ -624,8 +626,8 @@ template <int KT, int RC>
 static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                              const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                              int page_size, int n_seqs, int ntok, int H, int R, int r, float scale, int window,
-                             const PageBounds pb, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
-    const size_t smem = (size_t)(64 + 2 * KT) * (R + r + 8) * sizeof(bf16);
+                             const PageBounds pb, int splits, float* part_o, float* part_ml, int q_rows, cudaStream_t stream) {
+    const size_t smem = (size_t)(q_rows + 2 * KT) * (R + r + 8) * sizeof(bf16);
     auto kern = latent_attention_mma_kernel<KT, RC>;
     static bool attr_set = false;                        // per instantiation
     if (!attr_set) {
@@ -637,7 +639,7 @@ static int launch_latent_mma(const void* qcat, const void* pool, int pool_row, v
     dim3 grid((unsigned)chunks, (R + RC - 1) / RC, splits);
     return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qcat, (const bf16*)pool, pool_row,
                      (bf16*)out, cu_seqlens, positions, seq_of_token, page_table, max_pages, page_size, n_seqs, H, R, r,
-                     scale * 1.4426950408889634f, window, pb, part_o, part_ml);
+                     scale * 1.4426950408889634f, window, pb, part_o, part_ml, q_rows);
 }
 
 // Merge of the partial results of a split: one block per (token, head) row.
@@ -666,13 +668,21 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const float* part_o
 // How many shares of the keys a step's attention is cut into: 1 unless the step has too few CTAs to fill the
 // GPU (decode steps of small batches); bounded by the tiles a window holds and by `max_splits`.
 GG_API gg_latent_attention_mma_splits(int n_seqs, int ntok, int H, int R, int r, int window, int max_ctx) {
-    const long long ctas = (((long long)ntok * H + 63) / 64 + n_seqs) * ((R + 255) / 256);
-    if (ctas >= 148) return 1;
+    // CTAs that have rows: a decode step (one token a sequence) has ceil(H / 64) per sequence, a prompt about
+    // ntok * H / 64; each times the CTAs that share a wide latent's columns
+    const long long row_ctas = ntok == n_seqs ? (long long)n_seqs * ((H + 63) / 64) : ((long long)ntok * H + 63) / 64;
+    const long long ctas = row_ctas * ((R + 255) / 256);
     const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;
     const int kt = wide ? 64 : 32;
     const int keys = window > 0 && window < max_ctx ? window + 1 : max_ctx;
     const int tiles = (keys + kt - 1) / kt + 1;
-    long long s = (2 * 148 + ctas - 1) / ctas;
+    static int target = -1;                              // CTAs a step should have; GOGGUF_B200_LATENT_SPLIT_CTAS overrides
+    if (target < 0) {
+        const char* e = getenv("GOGGUF_B200_LATENT_SPLIT_CTAS");
+        target = e != nullptr && atoi(e) > 0 ? atoi(e) : 3 * 148 / 2;       // measured best of 1.5, 2, 3 and 4 per SM
+    }
+    if (ctas >= target) return 1;
+    long long s = (target + ctas - 1) / ctas;
     if (s > tiles) s = tiles;
     if (s > 32) s = 32;
     return s < 1 ? 1 : (int)s;
@@ -686,11 +696,12 @@ GG_API gg_latent_attention_mma_takes(int R, int r) {
 
 // qcat [T, H, R + r], pool [page][page_size][pool_row], out [T, H, R], all bfloat16; cu_seqlens [n_seqs + 1].
 // splits > 1: part_o [T * H, splits, R] and part_ml [T * H, splits, 2] (float32) take the shares' partial results
-// and a second kernel merges them.
+// and a second kernel merges them.  max_new: the most new tokens any sequence of the step brings.
 GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row, void* out, const int* cu_seqlens,
                                const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                                int page_size, int n_pages, int n_seqs, int ntok, int H, int R, int r, float scale,
-                               int window, int splits, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+                               int window, int splits, float* part_o, float* part_ml, int max_new, int* status,
+                               cudaStream_t stream) {
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (!gg_latent_attention_mma_takes(R, r) || H <= 0 || (pool_row % 8) || pool_row < R + r || page_size <= 0 ||
         (page_size % 64) || (((uintptr_t)qcat | (uintptr_t)pool | (uintptr_t)out) & 15))
@@ -698,8 +709,11 @@ GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row,
     const PageBounds pb{n_pages, status};
     const bool wide = (size_t)(64 + 2 * 64) * (R + r + 8) * sizeof(bf16) <= 200 * 1024;     // room for 64-key tiles
 #define GG_LM(KT, RC) launch_latent_mma<KT, RC>(qcat, pool, pool_row, out, cu_seqlens, positions, seq_of_token, page_table, \
-        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, splits, part_o, part_ml, stream)
-    if (splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr))) return GG_ERR_ARG;
+        max_pages, page_size, n_seqs, ntok, H, R, r, scale, window, pb, splits, part_o, part_ml, q_rows, stream)
+    if (splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr)) || max_new < 1) return GG_ERR_ARG;
+    // the most rows one CTA can have: 64, or all (token, head) pairs of the longest new stretch if those are fewer
+    const long long most = (long long)max_new * H;
+    const int q_rows = most >= 64 ? 64 : (int)((most + 15) / 16 * 16);
     int rc;
     if (R <= 64) rc = wide ? GG_LM(64, 64) : GG_LM(32, 64);
     else if (R <= 128) rc = wide ? GG_LM(64, 128) : GG_LM(32, 128);

@@ -218,7 +218,7 @@ def latent(sizes=((16, 64, 32, 64, 256, 1024, 2048), (32, 128, 64, 128, 512, 204
             po = torch.empty(B * H, S, R, device=dev)
             pml = torch.empty(B * H, S, 2, device=dev)
             us = _time_graph(lambda i: FL.latent_attention_mma(q1, pools[i % nrot], o1, cu1, pos1, sot1, tb, 64, B, B, H, R, r, 0.1,
-                                                               win, S, po, pml))
+                                                               win, S, po, pml, max_new=1))
             by = B * min(ctx, win) * D * 2
             print(f"latent_attention_mma decode B={B:3d} splits={S:2d} {tag}: {us:9.1f} us {by / us / 1e3:7.1f} GB/s {by / us / 1e3 / hbm:5.3f} of {of} copy bandwidth", flush=True)
             del pools

@@ -276,7 +276,7 @@ def test_latent_attention_kernels_agree_on_made_up_queries():
         q2[0::2] = q_b
         out2 = torch.full((B, H, R), float("nan"), dtype=torch.bfloat16, device=dev)
         fast_latent.latent_attention_mma(q2.to(dev), pool_b.to(dev), out2, cu2, pos2, sot2, table2, page_rows,
-                                         B, B, H, R, r, scale, window)
+                                         B, B, H, R, r, scale, window, max_new=1)
         assert rel_err(out2[0::2], want) < 8e-3
         assert torch.equal(out2[1::2].float().cpu(), torch.zeros(T, H, R))
         # the cached positions cut into shares whose partial results a second kernel merges (steps of few CTAs);
@@ -288,9 +288,11 @@ def test_latent_attention_kernels_agree_on_made_up_queries():
                 part_o = torch.full((ntok * H, splits, R), float("nan"), device=dev)
                 part_ml = torch.full((ntok * H, splits, 2), float("nan"), device=dev)
                 fast_latent.latent_attention_mma(qq.to(dev), pool_b.to(dev), outs, cuq, posq, sotq, tabq, page_rows,
-                                                 nseq, ntok, H, R, r, scale, window, splits, part_o, part_ml)
+                                                 nseq, ntok, H, R, r, scale, window, splits, part_o, part_ml,
+                                                 max_new=ntok if nseq == 1 else 1)
                 assert rel_err(outs[pick], want) < 8e-3, (H, R, r, window, splits)
     assert fast_latent.mma_splits(8, 8, 16, 128, 32, 1024, 4096) > 1 and fast_latent.mma_splits(1, 4096, 16, 128, 32, 1024, 4096) == 1
+    assert fast_latent.mma_splits(64, 64, 32, 512, 64, 2048, 4096) > 1
 
 
 def test_per_head_products_on_the_tensor_cores_equal_the_plain_ones():
