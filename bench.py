@@ -165,7 +165,7 @@ GIGOPEL_SIZES = {
 
 def gigopel_config(z, kind):
     mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
-                 scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=dict(base=250000.0, dims=z["rot_dim"]),
+                 scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=dict(base=500000.0, dims=z["rot_dim"]),
                  mask=dict(size=z["window"]))
     mlp = dict(kind="dense", ff=z["ff"]) if kind == "dense" else dict(
         kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"]))

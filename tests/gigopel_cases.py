@@ -56,11 +56,11 @@ CASE_ODD = dict(
     ])
 # wide enough for the tensor-core products of more than 128 tokens and for the experts' grouped products
 CASE_W = dict(
-    architecture="Gigopel", vocab=523, width=256, residual_mult=0.3, norm=dict(eps=1e-6),
+    architecture="Gigopel", vocab=523, width=256, residual_mult=0.35, norm=dict(eps=3e-6),
     layers=[
-        layer(mixer(8, 32, 32, 32, 128, 0.125, 250000.0, window=150), moe(128, 1.0, 6, 2)),
+        layer(mixer(8, 32, 32, 32, 128, 0.13, 100000.0, window=150), moe(128, 1.0, 6, 2)),
         layer(mixer(4, 64, 16, 64, 272, 0.11, 10000.0, window=90), dense(384)),
-        layer(mixer(8, 32, 32, 32, 128, 0.125, 250000.0, window=150), moe(64, 3.0, 9, 1)),
+        layer(mixer(8, 32, 32, 32, 128, 0.13, 100000.0, window=150), moe(64, 3.0, 9, 1)),
     ])
 CASES = {"T": (CASE_T, 3), "ONE": (CASE_ONE, 4), "ODD": (CASE_ODD, 5), "W": (CASE_W, 6)}
 

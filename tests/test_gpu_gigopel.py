@@ -461,7 +461,7 @@ def draw_case(seed: int) -> dict:
         rot_dim = r.choice([2, 8, 16, 32, 48])
         shapes.append(mixer(r.choice([1, 2, 3, 5, 8]), r.choice([4, 8, 16, 24, 40, 64]), rot_dim,
                             r.choice([4, 8, 16, 24, 56]), r.choice([8, 16, 32, 48, 80, 100, 144]),
-                            r.choice([0.05, 0.125, 0.3]), r.choice([100.0, 1e4, 250000.0]),
+                            r.choice([0.05, 0.11, 0.3]), r.choice([100.0, 1e4, 300000.0]),
                             dims=r.choice([d for d in (2, 4, 8, 16, 32, 48) if d <= rot_dim]),
                             window=r.choice([None, 1, 2, 17, 63, 64, 65, 128, 200])))
     for _ in range(r.choice([1, 2, 3, 4, 5])):
@@ -470,7 +470,7 @@ def draw_case(seed: int) -> dict:
         mlp = None if kind == "none" else dense(r.choice([8, 24, 40, 72, 200])) if kind == "dense" else \
             moe(r.choice([8, 16, 40, 96]), r.choice([0.5, 1.0, 4.0]), experts, r.randint(1, min(experts, 4)))
         layers.append(layer(r.choice(shapes), mlp))
-    return dict(architecture="Gigopel", vocab=r.choice([53, 211, 640, 1031]), width=width,
+    return dict(architecture="Gigopel", vocab=r.choice([53, 211, 641, 1031]), width=width,
                 residual_mult=r.choice([0.2, 0.5, 1.0, 1.3]), norm=dict(eps=r.choice([1e-6, 1e-5, 3e-4])), layers=layers)
 
 
