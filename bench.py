@@ -256,7 +256,7 @@ def compare_run(a):
         mats = H * (d + r) * W + (R + r) * W + H * (d + dv) * R + W * H * dv
         ff_active = 2 * W * z["ff"] if kind == "dense" else z["top"] * 3 * W * z["expert_ff"] + z["experts"] * W
         keys = sum(min(i + 1, win) for i in range(t))
-        attn = 2 * H * (2 * R + r) * keys                      # absorbed form: scores over R + r, values over R
+        attn = 2 * H * (d + r + dv) * keys                     # a whole prompt runs the expanded form: per-head keys and values
         flops = z["layers"] * (2 * t * (mats + ff_active) + attn) + 2 * z["vocab"] * W
         ff_read = 2 * W * z["ff"] if kind == "dense" else z["experts"] * 3 * W * z["expert_ff"]
         return flops, z["layers"] * (mats + ff_read) * 2 + z["vocab"] * W * 2

@@ -49,6 +49,26 @@ def mma_splits(n_seqs: int, n_tokens: int, heads: int, R: int, r: int, window: i
         int(n_seqs), int(n_tokens), heads, R, r, int(window), int(max_ctx)))
 
 
+def latent_prompt_mma(qd: torch.Tensor, qcat: torch.Tensor, kv: torch.Tensor, ckr: torch.Tensor, av: torch.Tensor,
+                      cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, n_seqs: int, n_tokens: int, heads: int,
+                      d: int, r: int, dv: int, R: int, scale: float, window: int, out_scale: float = 1.0) -> None:
+    """Attention of a step whose sequences all start at position 0, in the expanded form: qd [T, >= heads (d + r)]
+    (plain query parts), qcat [T, heads, R + r] (rotated parts at [..., R:]), kv [T, heads d + heads dv] (per-head
+    plain keys, then values), ckr [T, R + r] (the shared rotated key part at [:, R:]); av [T, heads, dv] receives
+    out_scale times the heads' outputs.  All bfloat16."""
+    for t in (qd, qcat, kv, ckr, av):
+        if t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+            raise KernelError("latent_prompt_mma takes bfloat16 rows")
+    kernel("latent_attention", "gg_latent_prompt_mma")(
+        qd.data_ptr(), qd.stride(0), qcat.data_ptr(), kv.data_ptr(), kv.stride(0), ckr.data_ptr(), ckr.stride(0),
+        av.data_ptr(), cu_seqlens.data_ptr(), seq_of_token.data_ptr(), int(n_seqs), int(n_tokens), heads, d, r, dv, R,
+        float(scale), int(window), float(out_scale), torch.cuda.current_stream().cuda_stream)
+
+
+def prompt_takes(d: int, r: int, dv: int) -> bool:
+    return bool(module("latent_attention").lib.gg_latent_prompt_mma_takes(int(d), int(r), int(dv)))
+
+
 def mma_takes(R: int, r: int) -> bool:
     return bool(module("latent_attention").lib.gg_latent_attention_mma_takes(int(R), int(r)))
 

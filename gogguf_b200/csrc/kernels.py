@@ -172,21 +172,24 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 def latent_prep(q: torch.Tensor, dkv: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos: torch.Tensor,
                 sin: torch.Tensor, rot_dims: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                 page_table: torch.Tensor, page_size: int, pool: Optional[torch.Tensor], qcat: torch.Tensor,
-                n_tokens: int, heads: int, d: int, r: int, R: int) -> None:
+                n_tokens: int, heads: int, d: int, r: int, R: int, dense: Optional[torch.Tensor] = None) -> None:
     """Norm of the latent, rotation of the shared key part and of the queries' rotated parts, cache write.
     q [T, heads * (d + r)] and dkv [T, R + r] may be column ranges of one buffer (row strides are passed);
-    pool [page][page_size][row]; qcat [T, heads, R + r] receives the rotated parts at [..., R:]."""
+    pool [page][page_size][row]; qcat [T, heads, R + r] receives the rotated parts at [..., R:]; dense (optional,
+    contiguous [T, R + r] in the cache's dtype) receives the rows the cache gets, token by token."""
     if q.dtype != dkv.dtype or (pool is not None and pool.dtype != q.dtype):
         raise KernelError("latent_prep: q, dkv and the cache must share one dtype")
     if q.stride(-1) != 1 or dkv.stride(-1) != 1 or not qcat.is_contiguous():
         raise KernelError("latent_prep: rows must be contiguous")
     _need(norm_weight, torch.float32, "norm weight")
+    if dense is not None and (dense.dtype != q.dtype or not dense.is_contiguous() or dense.shape[-1] != R + r):
+        raise KernelError("latent_prep: the dense copy is contiguous [T, R + r] in the dtype of q")
     from .tcgen05_gemm import status_word
     kernel("latent_attention", "gg_latent_prep")(
         _p(q), q.stride(0), _p(dkv), dkv.stride(0), dtype_code(q.dtype), _p(norm_weight), float(eps), _p(cos), _p(sin),
         int(rot_dims), _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], int(page_size),
         pool.shape[0] if pool is not None else 0, _p(pool), pool.shape[-1] if pool is not None else R + r,
-        _p(qcat), dtype_code(qcat.dtype), n_tokens, heads, d, r, R, _p(status_word(q.device)), _stream())
+        _p(qcat), dtype_code(qcat.dtype), n_tokens, heads, d, r, R, _p(dense), _p(status_word(q.device)), _stream())
 
 
 def headwise_gemm(x: torch.Tensor, ldx: int, hx: int, w: torch.Tensor, out: torch.Tensor, ldo: int, ho: int,

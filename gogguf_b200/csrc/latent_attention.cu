@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
     const T* q, long long ldq, const T* dkv, long long lddkv, const float* __restrict__ normw, float eps,
     const float* cosv, const float* sinv, int dims, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int max_pages, int page_size,
-    T* pool, int pool_row, TQ* qcat, int H, int d, int r, int R, const PageBounds pb) {
+    T* pool, int pool_row, TQ* qcat, int H, int d, int r, int R, const PageBounds pb, T* dense) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
@@ -56,17 +56,24 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
         }
         qc[(size_t)h * (R + r) + R + e] = from_f<TQ>(v);
     }
-    if (pool == nullptr) return;
+    if (pool == nullptr && dense == nullptr) return;
     const T* dk = dkv + (size_t)t * lddkv;
     float ss = 0.f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) { const float v = to_f<T>(dk[i]); ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     const float f = 1.0f / sqrtf(ss / (float)R + eps);
     const int pos = positions[t];
-    const int page = gg_page_w(page_table + (size_t)b * max_pages, pos / page_size, max_pages, pb, 49);
-    if (page < 0) return;
-    T* row = pool + ((size_t)page * page_size + (pos % page_size)) * pool_row;
-    for (int i = threadIdx.x; i < R; i += blockDim.x) row[i] = from_f<T>(to_f<T>(dk[i]) * f * normw[i]);
+    T* row = nullptr;
+    if (pool != nullptr) {
+        const int page = gg_page_w(page_table + (size_t)b * max_pages, pos / page_size, max_pages, pb, 49);
+        if (page >= 0) row = pool + ((size_t)page * page_size + (pos % page_size)) * pool_row;
+    }
+    T* drow = dense != nullptr ? dense + (size_t)t * (R + r) : nullptr;      // the same row, token by token
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const T v = from_f<T>(to_f<T>(dk[i]) * f * normw[i]);
+        if (row != nullptr) row[i] = v;
+        if (drow != nullptr) drow[i] = v;
+    }
     for (int e = threadIdx.x; e < r; e += blockDim.x) {
         float v = to_f<T>(dk[R + e]);
         if (e < dims) {
@@ -74,23 +81,25 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
             const float c = cs[e >> 1], s = sn[e >> 1];
             v = (e & 1) ? v * c + o * s : v * c - o * s;
         }
-        row[R + e] = from_f<T>(v);
+        if (row != nullptr) row[R + e] = from_f<T>(v);
+        if (drow != nullptr) drow[R + e] = from_f<T>(v);
     }
 }
 
 // q, dkv and the pool share `dtype`; qcat has `q_dtype`.  pool may be null (a layer that reads another's cache).
+// dense (may be null): [T, R + r] in `dtype`, the rows the cache gets, token by token.
 GG_API gg_latent_prep(const void* q, long long ldq, const void* dkv, long long lddkv, int dtype, const float* normw,
                       float eps, const float* cosv, const float* sinv, int dims, const int* positions,
                       const int* seq_of_token, const int* page_table, int max_pages, int page_size, int n_pages,
                       void* pool, int pool_row, void* qcat, int q_dtype, int ntok, int H, int d, int r, int R,
-                      int* status, cudaStream_t stream) {
+                      void* dense, int* status, cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (H <= 0 || d <= 0 || r <= 0 || R <= 0 || dims < 0 || dims > r || (dims & 1) || pool_row < R + r || page_size <= 0)
         return GG_ERR_ARG;
     const PageBounds pb{n_pages, status};
 #define GG_PREP(T, TQ) gg_launch(latent_prep_kernel<T, TQ>, dim3(ntok), dim3(256), 0, stream, 1, (const T*)q, ldq, \
         (const T*)dkv, lddkv, normw, eps, cosv, sinv, dims, positions, seq_of_token, page_table, max_pages, page_size, \
-        (T*)pool, pool_row, (TQ*)qcat, H, d, r, R, pb)
+        (T*)pool, pool_row, (TQ*)qcat, H, d, r, R, pb, (T*)dense)
     if (dtype == GG_F32 && q_dtype == GG_F32) GG_PREP(float, float);
     else if (dtype == GG_BF16 && q_dtype == GG_F32) GG_PREP(bf16, float);
     else if (dtype == GG_BF16 && q_dtype == GG_BF16) GG_PREP(bf16, bf16);
@@ -722,6 +731,246 @@ GG_API gg_latent_attention_mma(const void* qcat, const void* pool, int pool_row,
     if (rc != 0 || splits == 1) return rc;
     return gg_launch(latent_combine_kernel, dim3((unsigned)(ntok * H)), dim3(128), 0, stream, 1, (const float*)part_o,
                      (const float*)part_ml, (bf16*)out, seq_of_token, H, R, splits);
+}
+
+// ----------------------------------------------------------------------------- attention of whole prompts, expanded
+// A step in which every sequence starts at position 0 holds all the keys it reads among its own tokens, so the
+// per-head keys [W_uk,h c | k_r] and values W_uv,h c can be made once by a product (kv[t] = [all heads' plain keys |
+// all heads' values]) and attention runs in the ordinary form: per (query, key, head) d + r + dv multiply-adds
+// instead of 2 R + r, and O is only dv wide, so many warps share an SM.  A CTA takes 64 consecutive tokens of one
+// sequence and one head; key tiles of 64 tokens come from the step's own rows (no page table), the rotated key part
+// from the dense copy latent_prep leaves.  Scores, softmax and sums in float32; the output is written per head into
+// av[t, h, :] already multiplied by `out_scale`.
+template <int DVT>
+__global__ void __launch_bounds__(128) latent_prompt_mma_kernel(
+    const bf16* qd, long long ldq, const bf16* qcat, const bf16* kv, long long ldkv, const bf16* ckr, long long ldc,
+    bf16* av, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token, int n_seqs, int H, int d, int r,
+    int dv, int R, float scale_log2, int window, float out_scale) {
+    pdl_launch();
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int KT = 64;
+    const int dq = d + r, LQ = dq + 8, LV = dv + 8;
+    bf16* qs = reinterpret_cast<bf16*>(smraw);          // [64][LQ]
+    bf16* ks = qs + 64 * LQ;                            // [2][KT][LQ]
+    bf16* vs = ks + 2 * KT * LQ;                        // [2][KT][LV]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y;
+    int b = 0, chunk = blockIdx.x, t0 = 0, n_new = 0;
+    for (; b < n_seqs; ++b) {
+        t0 = cu_seqlens[b];
+        n_new = cu_seqlens[b + 1] - t0;
+        const int chunks = (n_new + 63) / 64;
+        if (chunk < chunks) break;
+        chunk -= chunks;
+    }
+    if (b >= n_seqs) return;
+    const int p0 = chunk * 64;                           // first position of this CTA's queries (positions start at 0)
+    const int rows_here = min(64, n_new - p0);
+    pdl_wait();
+    if (seq_of_token[t0] < 0) {                          // a padding sequence: zero rows
+        for (int i = tid; i < rows_here * dv; i += 128)
+            av[((size_t)(t0 + p0 + i / dv) * H + h) * dv + i % dv] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int p1 = p0 + rows_here - 1;
+    int key_lo = 0;
+    if (window > 0 && p0 - window + 1 > 0) key_lo = p0 - window + 1;
+    const int tile0 = key_lo / KT, ntiles = p1 / KT - tile0 + 1;
+    const int cq_plain = d / 8, cq = dq / 8, cv = dv / 8;
+
+    auto load_keys = [&](int tile, int stage) {
+        bf16* kd = ks + (size_t)stage * KT * LQ;
+        bf16* vd = vs + (size_t)stage * KT * LV;
+        const int j0 = tile * KT;
+        for (int kk = warp; kk < KT; kk += 4) {
+            const int j = j0 + kk;
+            bf16* dk = kd + kk * LQ;
+            bf16* dvp = vd + kk * LV;
+            if (j <= p1) {
+                const bf16* kp = kv + (size_t)(t0 + j) * ldkv + (size_t)h * d;           // this head's plain key
+                const bf16* kr = ckr + (size_t)(t0 + j) * ldc + R;                       // the shared rotated part
+                const bf16* vp = kv + (size_t)(t0 + j) * ldkv + (size_t)H * d + (size_t)h * dv;
+                for (int c = lane; c < cq; c += 32)
+                    cp_async16(dk + c * 8, c < cq_plain ? kp + c * 8 : kr + (c - cq_plain) * 8);
+                for (int c = lane; c < cv; c += 32) cp_async16(dvp + c * 8, vp + c * 8);
+            } else {
+                for (int c = lane; c < cq; c += 32) zero16(dk + c * 8);
+                for (int c = lane; c < cv; c += 32) zero16(dvp + c * 8);
+            }
+        }
+    };
+    for (int row = warp; row < 64; row += 4) {           // queries: plain part from the product, rotated part from prep
+        bf16* dst = qs + row * LQ;
+        if (row < rows_here) {
+            const bf16* qp = qd + (size_t)(t0 + p0 + row) * ldq + (size_t)h * dq;
+            const bf16* qr = qcat + ((size_t)(t0 + p0 + row) * H + h) * (R + r) + R;
+            for (int c = lane; c < cq; c += 32) cp_async16(dst + c * 8, c < cq_plain ? qp + c * 8 : qr + (c - cq_plain) * 8);
+        } else {
+            for (int c = lane; c < cq; c += 32) zero16(dst + c * 8);
+        }
+    }
+    load_keys(tile0, 0);
+    cp_async_commit();
+
+    const int g = lane >> 2, q4 = lane & 3;
+    int prow[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int rr = warp * 16 + g + 8 * i;
+        valid[i] = rr < rows_here;
+        prow[i] = p0 + rr;
+    }
+    float o[DVT / 8][4];
+#pragma unroll
+    for (int i = 0; i < DVT / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    const int ksteps = dq / 16;
+
+    for (int it = 0; it < ntiles; ++it) {
+        if (it + 1 < ntiles) {
+            load_keys(tile0 + it + 1, (it + 1) & 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (warp * 16 < rows_here) {
+            const bf16* kt = ks + (size_t)(it & 1) * KT * LQ;
+            const bf16* vt = vs + (size_t)(it & 1) * KT * LV;
+            float s[KT / 8][4];
+#pragma unroll
+            for (int i = 0; i < KT / 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+            for (int kk = 0; kk < ksteps; ++kk) {
+                uint32_t a[4];
+                ldsm_x4(a, qs + (warp * 16 + (lane & 15)) * LQ + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int np = 0; np < KT / 16; ++np) {
+                    uint32_t bb[4];
+                    ldsm_x4(bb, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LQ + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma16816(s[2 * np], a, bb[0], bb[1]);
+                    mma16816(s[2 * np + 1], a, bb[2], bb[3]);
+                }
+            }
+            const int j0 = (tile0 + it) * KT;
+            float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+            for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int j = j0 + nt * 8 + 2 * q4 + (e & 1);
+                    const bool see = valid[i] && j <= prow[i] && (window <= 0 || j > prow[i] - window);
+                    const float v = see ? s[nt][e] * scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    mnew[i] = fmaxf(mnew[i], v);
+                }
+            float corr[2], muse[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 1));
+                mnew[i] = fmaxf(mnew[i], __shfl_xor_sync(0xffffffffu, mnew[i], 2));
+                muse[i] = mnew[i] == -INFINITY ? 0.f : mnew[i];
+                corr[i] = exp2f(mrow[i] - muse[i]);
+                mrow[i] = mnew[i];
+                lrow[i] *= corr[i];
+            }
+            uint32_t pfrag[KT / 16][4];
+#pragma unroll
+            for (int nt = 0; nt < KT / 8; ++nt) {
+                const float p0f = exp2f(s[nt][0] - muse[0]), p1f = exp2f(s[nt][1] - muse[0]);
+                const float p2f = exp2f(s[nt][2] - muse[1]), p3f = exp2f(s[nt][3] - muse[1]);
+                lrow[0] += p0f + p1f;
+                lrow[1] += p2f + p3f;
+                pfrag[nt >> 1][(nt & 1) * 2] = pack_bf16(p0f, p1f);
+                pfrag[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2f, p3f);
+            }
+#pragma unroll
+            for (int i = 0; i < DVT / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < KT / 16; ++kk) {
+#pragma unroll
+                for (int np = 0; np < DVT / 16; ++np) {
+                    if (np * 16 < dv) {
+                        uint32_t bb[4];
+                        ldsm_x4_trans(bb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LV + np * 16 + (lane >> 4) * 8);
+                        mma16816(o[2 * np], pfrag[kk], bb[0], bb[1]);
+                        mma16816(o[2 * np + 1], pfrag[kk], bb[2], bb[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
+        lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!valid[i]) continue;
+        const float inv = out_scale / lrow[i];
+        bf16* orow = av + ((size_t)(t0 + prow[i]) * H + h) * dv;
+#pragma unroll
+        for (int nt = 0; nt < DVT / 8; ++nt) {
+            const int c = nt * 8 + 2 * q4;
+            if (c < dv) *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+        }
+    }
+}
+
+// Does the expanded prompt kernel take these sizes?  Plain, rotated and value sizes whose rows and split points fall
+// on 16-byte boundaries, d + r and dv multiples of 16, dv at most 128, d + r at most 256.
+GG_API gg_latent_prompt_mma_takes(int d, int r, int dv) {
+    return (d > 0 && r > 0 && dv > 0 && d % 8 == 0 && r % 8 == 0 && (d + r) % 16 == 0 && dv % 16 == 0 && dv <= 128 &&
+            d + r <= 256) ? 1 : 0;
+}
+
+// qd [T, >= H (d + r)] (row stride ldq; head h's plain query at h (d + r)), qcat [T, H, R + r] (rotated query parts
+// at [..., R:]), kv [T, H d + H dv] (row stride ldkv), ckr [T, R + r] (row stride ldc; rotated key part at R),
+// av [T, H, dv]; every sequence of the step starts at position 0.
+GG_API gg_latent_prompt_mma(const void* qd, long long ldq, const void* qcat, const void* kv, long long ldkv,
+                            const void* ckr, long long ldc, void* av, const int* cu_seqlens, const int* seq_of_token,
+                            int n_seqs, int ntok, int H, int d, int r, int dv, int R, float scale, int window,
+                            float out_scale, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (!gg_latent_prompt_mma_takes(d, r, dv) || H <= 0 || H > 65535 || (ldq % 8) || (ldkv % 8) || (ldc % 8) ||
+        ((R + r) % 8) || (R % 8) || ((H * d) % 8) ||
+        (((uintptr_t)qd | (uintptr_t)qcat | (uintptr_t)kv | (uintptr_t)ckr | (uintptr_t)av) & 15))
+        return GG_ERR_ARG;
+    const size_t smem = ((size_t)(64 + 2 * 64) * (d + r + 8) + (size_t)2 * 64 * (dv + 8)) * sizeof(bf16);
+    dim3 grid((unsigned)(ntok / 64 + n_seqs), H);
+    const float sl2 = scale * 1.4426950408889634f;
+    if (dv <= 64) {
+        auto kern = latent_prompt_mma_kernel<64>;
+        static bool set = false;
+        if (!set) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            set = true;
+        }
+        return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qd, ldq, (const bf16*)qcat, (const bf16*)kv,
+                         ldkv, (const bf16*)ckr, ldc, (bf16*)av, cu_seqlens, seq_of_token, n_seqs, H, d, r, dv, R, sl2, window,
+                         out_scale);
+    }
+    auto kern = latent_prompt_mma_kernel<128>;
+    static bool set2 = false;
+    if (!set2) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        set2 = true;
+    }
+    return gg_launch(kern, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)qd, ldq, (const bf16*)qcat, (const bf16*)kv, ldkv,
+                     (const bf16*)ckr, ldc, (bf16*)av, cu_seqlens, seq_of_token, n_seqs, H, d, r, dv, R, sl2, window, out_scale);
 }
 
 GG_API gg_latent_attention_checked() { return gg_debug_bounds(); }

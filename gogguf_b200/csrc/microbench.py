@@ -185,6 +185,12 @@ def latent(sizes=((16, 64, 32, 64, 256, 1024, 2048), (32, 128, 64, 128, 512, 204
         fl = 2 * H * (2 * R + r) * keys
         print(f"latent_attention_mma prompt 2048  {tag}: {us:9.1f} us {fl / us / 1e6:7.1f} TFLOP/s {fl / us / 1e6 / tf:5.3f} of {of} bf16 peak", flush=True)
         qd = (torch.randn(T, H * (d + r) + D, device=dev) * 0.2).to(torch.bfloat16)
+        kvx = (torch.randn(T, H * (d + dv), device=dev) * 0.3).to(torch.bfloat16)
+        ckr = (torch.randn(T, D, device=dev) * 0.3).to(torch.bfloat16)
+        avx = torch.empty(T, H, dv, device=dev, dtype=torch.bfloat16)
+        us = _time_graph(lambda i: FL.latent_prompt_mma(qd, qcat, kvx, ckr, avx, cu, sot, 1, T, H, d, r, dv, R, 0.1, win, 0.5), 10)
+        fl = 2 * H * (d + r + dv) * keys
+        print(f"latent_prompt_mma (expanded) prompt 2048 {tag} d={d} dv={dv}: {us:9.1f} us {fl / us / 1e6:7.1f} TFLOP/s {fl / us / 1e6 / tf:5.3f} of {of} bf16 peak", flush=True)
         uk_t = (torch.randn(H, R, d, device=dev) * 0.1).to(torch.bfloat16)
         uv = (torch.randn(H, dv, R, device=dev) * 0.1).to(torch.bfloat16)
         av = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)

@@ -235,6 +235,7 @@ class Stepper:
             max_new=max(counts) if counts else 1,
             max_ctx=max((cache.lengths[s] + n for s, n in zip(slots, counts)), default=1),
             decode=all(n == 1 for n in counts),
+            fresh=bool(entries) and all(cache.lengths[e.slot] == 0 for e in entries),
         )
         return ctx, lay, lay.view(dev, "logit_rows")
 

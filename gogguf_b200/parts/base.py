@@ -80,6 +80,8 @@ class StepContext:
     max_ctx: int                  # longest sequence after this step (host; an upper bound under a graph)
     decode: bool                  # every sequence brings exactly one token
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
+    fresh: bool = False           # every sequence of the step starts at position 0 (whole prompts): what a token
+    #                               reads is among the step's own tokens
 
 
 class RowStats:

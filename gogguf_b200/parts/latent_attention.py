@@ -11,8 +11,11 @@ Only c and the rotated k_r are cached (`LatentRequest`: latent_dim + rope_dim nu
 whatever the number of heads).  Since key and value are linear in c, the step never builds them: the query's
 plain part is taken through Wuk_h^T once per token and head (the *absorbed* query, latent_dim wide), attention
 runs over the cached rows with all heads sharing every row it reads, and Wuv_h is applied to the weighted sum
-of latents afterwards.  One formulation serves prompts, portions of prompts and decoding, so a position's
-result does not depend on how its sequence was cut into steps.
+of latents afterwards.  That formulation serves prompts, portions of prompts and decoding alike.  A step in which
+every sequence starts at position 0 (whole prompts) may instead build the step's keys and values once by a
+product and run attention in the ordinary per-head form, which costs a third of the arithmetic; both forms
+compute the same sums, so a position's result does not depend on how its sequence was cut into steps beyond
+rounding.
 
 The rotation is the adjacent-pair kind (`rope_adjacent`), applied to the first `rotary_dim` elements of the
 rot part.  Spec parameters: hidden_size, num_heads, nope_dim, rope_dim, value_dim, latent_dim, scale, window,
@@ -30,6 +33,8 @@ from ..csrc import kernels as K
 from ..weights.loader import TensorDecl
 from .base import Linear, Runtime, StepContext
 from .registry import POSITIONS, lookup, register_mixer
+
+PROMPT_FORM_MIN_TOKENS = 32      # whole prompts of at least this many tokens take the expanded form
 
 _NAMES = dict(q="q_proj.weight", down="kv_down_proj.weight", latent_norm="kv_norm.weight", up_k="k_up_proj.weight",
               up_v="v_up_proj.weight", out="o_proj.weight")
@@ -91,9 +96,15 @@ class LatentAttentionMixer:
         self.o = Linear(weights[n["out"]], rt)
         self.out_scale = 1.0
         self._fast = None
+        self.kv_up = None
         if rt.fast and rt.dtype == torch.bfloat16 and self.uk_t.dtype == torch.bfloat16:
             from ..csrc import fast_latent
             self._fast = fast_latent.try_make(H, d, R, r, self.nq + R + r, self.scale, self.window)
+            # whole prompts: keys and values of all heads by one product, attention in the expanded form
+            if (self._fast is not None and fast_latent.prompt_takes(d, r, dv) and R % 8 == 0 and (H * d) % 8 == 0
+                    and (H * dv) % 8 == 0):
+                kv_up = Linear(torch.cat([rt.matrix(weights[n["up_k"]]), rt.matrix(weights[n["up_v"]])], dim=0), rt)
+                self.kv_up = kv_up if kv_up.tensor_core else None
 
     def scale_output(self, mult: float) -> bool:
         """Multiply what this part adds to the residual by `mult`: the factor goes onto the heads' outputs in
@@ -117,6 +128,20 @@ class LatentAttentionMixer:
         qcat = ctx.ws.get("lat_qcat", (T, H, R + r), mid)
         cos, sin = self.position.tables(ctx)
         table = ctx.page_tables[cache.group]
+        av = ctx.ws.get("lat_values", (T, H * dv), dt)
+        if self.kv_up is not None and ctx.fresh and ctx.max_new >= PROMPT_FORM_MIN_TOKENS:
+            # every sequence starts at position 0: what a token reads is among the step's own tokens
+            from ..csrc import fast_latent
+            ckr = ctx.ws.get("lat_rows_dense", (T, R + r), dt)
+            K.latent_prep(qd[:, :self.nq], qd[:, self.nq:], self.latent_norm, self.eps, cos, sin, self.rot,
+                          ctx.positions, ctx.seq_of_token, table, cache.page_size,
+                          cache.pool if writes_cache else None, qcat, T, H, d, r, R, dense=ckr)
+            kv = ctx.ws.get("lat_keys_values", (T, H * (d + dv)), dt)
+            self.kv_up(ckr[:, :R], kv, ws=ctx.ws)
+            fast_latent.latent_prompt_mma(qd, qcat, kv, ckr, av, ctx.cu_seqlens, ctx.seq_of_token, ctx.n_seqs, T, H, d, r,
+                                          dv, R, self.scale, self.window, self.out_scale)
+            self.o(av, residual, accumulate=True, ws=ctx.ws)
+            return
         K.latent_prep(qd[:, :self.nq], qd[:, self.nq:], self.latent_norm, self.eps, cos, sin, self.rot,
                       ctx.positions, ctx.seq_of_token, table, cache.page_size, cache.pool if writes_cache else None,
                       qcat, T, H, d, r, R)
@@ -130,7 +155,6 @@ class LatentAttentionMixer:
         else:
             K.latent_attention_plain(qcat, cache.pool, olat, ctx.positions, ctx.seq_of_token, table,
                                      cache.page_size, T, H, R, r, self.scale, self.window)
-        av = ctx.ws.get("lat_values", (T, H * dv), dt)
         if self._fast is not None:
             self._fast.expand(olat, self.uv, av, T, self.out_scale)
         else:

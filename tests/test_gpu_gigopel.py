@@ -514,3 +514,52 @@ def test_a_configuration_nobody_chose(tmp_path, seed):
         cache_g.close(b)
         cache_g.check()
         assert close(torch.stack(rows), torch.stack(refs), dtype), (json.dumps(cfg), dtype)
+
+
+def test_prompt_attention_in_the_expanded_form_against_a_loop():
+    """Several sequences that start at position 0 (one of a single token, one padding sequence between them), queries
+    made to ask for one key each: the window's first and last position, the tile borders, the token itself."""
+    from gogguf_b200.csrc import fast_latent
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(11)
+    for H, d, r, dv, R, window in ((3, 24, 8, 16, 40, 37), (2, 64, 32, 64, 64, 130), (4, 128, 64, 128, 96, 0), (1, 8, 8, 32, 16, 64)):
+        assert fast_latent.prompt_takes(d, r, dv)
+        lens = [200, 1, 0, 77]                               # 0: a padding sequence of one row
+        rows = [n if n else 1 for n in lens]
+        T = sum(rows)
+        cu = [0]
+        for n in rows:
+            cu.append(cu[-1] + n)
+        sot = []
+        for b, n in enumerate(lens):
+            sot += [b if n else -1] * (n if n else 1)
+        ldq = H * (d + r) + R + r
+        qd = torch.zeros(T, ldq)
+        qcat = torch.zeros(T, H, R + r)
+        kv = torch.randn(T, H * d + H * dv, generator=g)
+        ckr = torch.randn(T, R + r, generator=g)
+        want = torch.zeros(T, H, dv, dtype=torch.float64)
+        scale = 0.5
+        kvb, ckrb = kv.to(torch.bfloat16), ckr.to(torch.bfloat16)
+        for b, n in enumerate(lens):
+            t0 = cu[b]
+            for p in range(n):
+                for h in range(H):
+                    keys = torch.cat([kvb[t0:t0 + n, h * d:(h + 1) * d], ckrb[t0:t0 + n, R:]], dim=1).double()
+                    choice = [p, max(0, p - window + 1) if window else 0, max(0, p - window) if window else p // 3,
+                              (p // 64) * 64, max(0, (p // 64) * 64 - 1)][(p + h) % 5]
+                    q = (keys[choice] * (24.0 / float(keys[choice].norm() ** 2))).float()
+                    qd[t0 + p, h * (d + r):h * (d + r) + d] = q[:d]
+                    qcat[t0 + p, h, R:] = q[d:]
+                    qb = torch.cat([qd[t0 + p, h * (d + r):h * (d + r) + d], qcat[t0 + p, h, R:]]).to(torch.bfloat16).double()
+                    lo = max(0, p - window + 1) if window else 0
+                    s = (keys[lo:p + 1] @ qb) * scale
+                    vals = kvb[t0 + lo:t0 + p + 1, H * d + h * dv:H * d + (h + 1) * dv].double()
+                    want[t0 + p, h] = 0.7 * (torch.softmax(s, 0) @ vals)
+        ints = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        av = torch.full((T, H, dv), float("nan"), dtype=torch.bfloat16, device=dev)
+        fast_latent.latent_prompt_mma(qd.to(torch.bfloat16).to(dev), qcat.to(torch.bfloat16).to(dev), kvb.to(dev), ckrb.to(dev),
+                                      av, ints(cu), ints(sot), len(lens), T, H, d, r, dv, R, scale, window, 0.7)
+        live = torch.tensor([s >= 0 for s in sot])
+        assert rel_err(av[live], want[live]) < 8e-3, (H, d, r, dv, R, window)
+        assert float(av[~live].float().abs().max()) == 0.0
