@@ -15,7 +15,8 @@
 //
 // Kernels here: latent_prep, headwise_gemm (the per-head products, CUDA cores, any dtype mix),
 // latent_attention_plain (one block per token and head, float32 arithmetic: the 32-bit path and the twin of
-// the tensor-core kernel), and latent_attention_mma (bfloat16, mma.sync, 64 query rows per CTA).
+// the tensor-core kernel), latent_attention_mma (bfloat16, mma.sync, 64 query rows per CTA), and
+// latent_prompt_mma: whole prompts in the expanded form (per-head keys and values built by a product).
 // Scores, softmax, the norm and the rotation are float32 in all of them.
 #include "common.cuh"
 
