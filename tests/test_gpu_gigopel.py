@@ -563,3 +563,67 @@ def test_prompt_attention_in_the_expanded_form_against_a_loop():
         live = torch.tensor([s >= 0 for s in sot])
         assert rel_err(av[live], want[live]) < 8e-3, (H, d, r, dv, R, window)
         assert float(av[~live].float().abs().max()) == 0.0
+
+
+def test_prep_norm_rotation_and_cache_write_alone():
+    """latent_prep against the plain norm and rotation: a partial rotation, pages out of order, a padding token, the
+    dense copy, and no other row of the pool touched."""
+    from gogguf_b200.csrc import kernels as K
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(13)
+    H, d, r, R, dims, base, eps = 3, 10, 12, 20, 8, 777.0, 1e-5
+    T = 7
+    pos = torch.tensor([62, 63, 64, 65, 0, 130, 5])
+    sot = [0, 0, 0, 0, -1, 1, 1]
+    q = torch.randn(T, H * (d + r), generator=g)
+    dkv = torch.randn(T, R + r, generator=g)
+    nw = torch.rand(R, generator=g) + 0.5
+    half = dims // 2
+    ang = pos.double()[:, None] * (base ** (-2.0 * torch.arange(half).double() / dims))[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    row = 40                                                  # pool rows wider than R + r
+    pool = torch.full((6, 64, row), 9.0)
+    table = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
+    qcat = torch.full((T, H, R + r), 7.0)
+    dense = torch.full((T, R + r), 7.0)
+    pool_d, qcat_d, dense_d = pool.to(dev), qcat.to(dev), dense.to(dev)
+    K.latent_prep(q.to(dev), dkv.to(dev), nw.to(dev), eps, cos.to(dev), sin.to(dev), dims,
+                  pos.to(torch.int32).to(dev), torch.tensor(sot, dtype=torch.int32, device=dev), table.to(dev), 64, pool_d,
+                  qcat_d, T, H, d, r, R, dense=dense_d)
+    c = plain.wnorm(dkv[:, :R].double(), nw, eps)
+    kr = plain.rotate_adjacent(dkv[:, R:].double(), pos, base, dims)
+    qr = plain.rotate_adjacent(q.view(T, H, d + r)[..., d:].double(), pos, base, dims)
+    want_pool = pool.clone().double()
+    for t in range(T):
+        if sot[t] < 0:
+            continue
+        page = int(table[sot[t], int(pos[t]) // 64])
+        want_pool[page, int(pos[t]) % 64, :R] = c[t]
+        want_pool[page, int(pos[t]) % 64, R:R + r] = kr[t]
+        assert rel_err(qcat_d[t, :, R:], qr[t]) < 1e-6
+        assert rel_err(dense_d[t], torch.cat([c[t], kr[t]])) < 1e-6
+        assert float((qcat_d[t, :, :R].cpu() - 7.0).abs().max()) == 0.0       # the absorbed part is another kernel's
+    assert float(qcat_d[4, :, R:].abs().max()) == 0.0                          # the padding token: zeros, no cache row
+    assert rel_err(pool_d, want_pool) < 1e-6
+    assert int((pool_d.cpu() != 9.0).sum()) == 6 * (R + r)                      # six rows written, nothing else
+
+
+def test_a_part_without_a_factor_of_its_own_gets_it_from_the_block(tmp_path_factory, monkeypatch):
+    """The parallel block hands a part that cannot take the residual factor a zeroed buffer and adds factor times
+    the buffer itself; the result is the one of parts that take the factor into their last product."""
+    from gogguf_b200.parts.experts import RoutedExperts, XieluMLP
+    from gogguf_b200.parts.latent_attention import LatentAttentionMixer
+    folder = make_folder(tmp_path_factory.getbasetemp(), "T", "float32")
+    cfg, w = read_folder(folder)
+    tokens = random_tokens(cfg["vocab"], 90, seed=3)
+    want = plain_logits(cfg, w, tokens)
+    model, cache, st = load(folder, "float32")
+    assert all(all(b._direct.values()) for b in model.blocks)
+    direct = run_cut(st, cache, tokens, [90])
+    for cls in (LatentAttentionMixer, XieluMLP, RoutedExperts):
+        monkeypatch.setattr(cls, "scale_output", lambda self, mult: False)
+    model2, cache2, st2 = load(folder, "float32")
+    assert not any(any(b._direct.values()) for b in model2.blocks)
+    through_buffer = run_cut(st2, cache2, tokens, [60, 30])
+    assert rel_err(direct, want) < TOL_F32 and rel_err(through_buffer, want) < TOL_F32
+    assert not torch.equal(direct, through_buffer)
