@@ -627,3 +627,49 @@ def test_a_part_without_a_factor_of_its_own_gets_it_from_the_block(tmp_path_fact
     through_buffer = run_cut(st2, cache2, tokens, [60, 30])
     assert rel_err(direct, want) < TOL_F32 and rel_err(through_buffer, want) < TOL_F32
     assert not torch.equal(direct, through_buffer)
+
+
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("W", "bfloat16"), ("ODD", "float32")])
+def test_trace_replay_through_the_program(tmp_path_factory, tmp_path, name, dtype):
+    """bin/trace_run, the program a user runs: requests whole, with their last tokens one by one, and a batch of
+    unequal lengths decoded together while the shorter ones end; places where nothing is wanted; a cache that two
+    batches do not fit into at once."""
+    from test_gpu_replay import Trace
+    folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
+    cfg, w = read_folder(folder)
+    lens = [150, 33, 97, 1]
+    reqs = {f"r{i}": random_tokens(cfg["vocab"], n, seed=40 + i) for i, n in enumerate(lens)}
+    oracle = {k: plain_logits(cfg, w, t) for k, t in reqs.items()}
+    got_rows, want_rows = [], []
+    tr = Trace(folder, dtype, tmp_path / "out", max_tokens=192 + 64 + 128 + 64)
+    try:
+        for k, t in reqs.items():                                        # whole, a few places wanted
+            want = sorted({0, len(t) // 2, len(t) - 1})
+            got = tr.step([{"id": k + "w", "tokens": t, "want": want}], end=[k + "w"])
+            got_rows.append(torch.from_numpy(got)); want_rows.append(oracle[k][want])
+        t = reqs["r0"]                                                   # the tail one by one
+        cut = len(t) - 40
+        assert tr.step([{"id": "d", "tokens": t[:cut], "want": []}]) is None
+        for i in range(cut, len(t)):
+            got = tr.step([{"id": "d", "tokens": [t[i]], "want": [0] if i % 3 else []}], end=["d"] if i == len(t) - 1 else [])
+            if i % 3:
+                got_rows.append(torch.from_numpy(got)); want_rows.append(oracle["r0"][i:i + 1])
+        batch = ["r3", "r1", "r2", "r0"]                                 # together; the shorter ones end earlier
+        pre = {k: max(1, len(reqs[k]) - 12) for k in batch}
+        got = tr.step([{"id": k + "b", "tokens": reqs[k][:pre[k]], "want": [pre[k] - 1]} for k in batch],
+                      end=[k + "b" for k in batch if pre[k] == len(reqs[k])])
+        for j, k in enumerate(batch):
+            got_rows.append(torch.from_numpy(got[j:j + 1])); want_rows.append(oracle[k][pre[k] - 1:pre[k]])
+        pos = dict(pre)
+        live = [k for k in batch if pre[k] < len(reqs[k])]
+        while live:
+            ending = [k for k in live if pos[k] + 1 == len(reqs[k])]
+            got = tr.step([{"id": k + "b", "tokens": [reqs[k][pos[k]]], "want": [0]} for k in live],
+                          end=[k + "b" for k in ending])
+            for j, k in enumerate(live):
+                got_rows.append(torch.from_numpy(got[j:j + 1])); want_rows.append(oracle[k][pos[k]:pos[k] + 1])
+                pos[k] += 1
+            live = [k for k in live if k not in ending]
+    finally:
+        tr.close()
+    assert close(torch.cat(got_rows), torch.cat(want_rows), dtype)
