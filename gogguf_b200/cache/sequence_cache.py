@@ -2,17 +2,21 @@
 
 What each scheduled layer needs is asked of its mixer as a *request*:
 
-* `KVRequest(num_kv_heads, head_dim, window)` - keys and values of every position (window None)
-  or of the last `window` positions.  Layers with equal requests form a *group* with storage of
-  its own: pools ``k, v [layer_in_group][page][kv_head][page_size][head_dim]`` and, per slot, the
-  list of pages that hold its positions.  A windowed group gives pages back as soon as every
-  position in them has left the window.
+* `KVRequest(num_kv_heads, head_dim, window, value_dim)` - keys and values of every position
+  (window None) or of the last `window` positions.  Layers with equal requests form a *group* with
+  storage of its own: pools ``k [layer_in_group][page][kv_head][page_size][head_dim]``, ``v`` alike
+  with `value_dim` (the head size of the keys unless given) and, per slot, the list of pages that
+  hold its positions.  A windowed group gives pages back as soon as every position in them has left
+  the window.
 * `LatentRequest(width, window)` - one vector per position (latent attention caches its compressed
   key/value vector and the shared rotated key part instead of per-head keys and values); paged and
   windowed like the above, pool ``[layer_in_group][page][page_size][width]``.
 * `StateRequest(shape, dtype)` - a fixed-size state per sequence, ``[max_slots, *shape]`` for that
   layer, zeroed when a slot is opened.
 * None - the layer keeps nothing.
+* a tuple of requests - a mixer made of several mixers asks for one cache or state per member; each
+  member's request is grouped and stored as if a layer of its own had made it, and the layer is
+  handed the tuple of their views.
 
 A sequence's length lives here once, for all groups; a step first *plans* (checks capacity and
 reserves pages for the tokens it brings, all or nothing), the kernels write keys and values at
@@ -49,6 +53,7 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None      # head size of the values where it differs from the keys'
 
 
 @dataclass(frozen=True)
@@ -114,6 +119,15 @@ class CacheStore:
         pass
 
     def check(self, is_open) -> None:             # bookkeeping invariants, for tests
+        pass
+
+    def save(self, slots: Sequence[int]):
+        """What a step would change for these slots beyond writing its own positions, for `load` to put back:
+        a caller that runs a step twice (a warm-up before a graph capture) brackets the first run with the two.
+        Per-position storage needs nothing (the second run writes the same rows again)."""
+        return None
+
+    def load(self, saved) -> None:
         pass
 
 
@@ -214,10 +228,10 @@ class KVGroup(PagedStore):
     def __init__(self, request: KVRequest, entries: List[int], n_pages: int, page_size: int,
                  dtype: torch.dtype, device, max_slots: int = 0):
         super().__init__(request, entries, n_pages, page_size, window=request.window)
-        shape = (len(entries), n_pages, request.num_kv_heads, page_size, request.head_dim)
+        lead = (len(entries), n_pages, request.num_kv_heads, page_size)
         # zero-filled once: a page that is handed out again holds old finite numbers, never NaN patterns
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.k = torch.zeros(lead + (request.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(lead + (request.value_dim or request.head_dim,), dtype=dtype, device=device)
 
     def view(self, entry: int) -> "KVView":
         li = self.entries.index(entry)
@@ -229,7 +243,7 @@ class KVView:
     """What a mixer gets for one scheduled layer: its slices of the group's pools."""
     group: int
     k: torch.Tensor            # [page][kv_head][page_size][head_dim]
-    v: torch.Tensor
+    v: torch.Tensor            # [page][kv_head][page_size][value_dim]
     page_size: int
     request: KVRequest
 
@@ -299,6 +313,14 @@ class StateStore(CacheStore):
     def can_shorten(self, slot: int, length: int) -> bool:
         return False
 
+    def save(self, slots: Sequence[int]):
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.state.device)
+        return idx, self.state.index_select(0, idx)
+
+    def load(self, saved) -> None:
+        idx, rows = saved
+        self.state.index_copy_(0, idx, rows)
+
 
 class SequenceCache:
     def __init__(self, requests: Sequence[Request], cache_of: Sequence[Optional[int]], max_tokens: int,
@@ -319,25 +341,40 @@ class SequenceCache:
         self.stores: List[CacheStore] = []        # every store, paged or not
         self.groups: List[PagedStore] = []        # the paged ones, in the order of their page tables
         self._views: Dict[int, object] = {}
-        shared: Dict[Tuple[type, object], List[int]] = {}
-        own: List[Tuple[type, object, List[int]]] = []
+        # a store's "entry" is a schedule entry i, or (i, k) for member k of a tuple of requests
+        shared: Dict[Tuple[type, object], list] = {}
+        own: List[Tuple[type, object, list]] = []
+        member_views: Dict[object, object] = {}
+        tuples: Dict[int, int] = {}
+        single: Dict[object, object] = {}
         for i, (rq, src) in enumerate(zip(requests, cache_of)):
             if src is not None:
                 continue
             if rq is None:
                 self._views[i] = None
                 continue
-            store_cls = STORES.get(type(rq))
-            if store_cls is None:
-                raise CacheError(f"schedule entry {i}: no store is registered for cache requests of type "
-                                 f"{type(rq).__name__} (registered: {sorted(c.__name__ for c in STORES)})")
-            key = store_cls.group_key(rq)
-            if key is None:
-                own.append((store_cls, rq, [i]))
+            if isinstance(rq, (tuple, list)):
+                tuples[i] = len(rq)
+                members = [((i, k), r) for k, r in enumerate(rq)]
             else:
-                shared.setdefault((store_cls, key), []).append(i)
-        built = [(cls, requests[entries[0]], entries) for (cls, _), entries in shared.items()] + own
-        for store_cls, rq, entries in sorted(built, key=lambda b: b[2][0]):
+                members = [(i, rq)]
+            for entry, r in members:
+                if r is None:
+                    member_views[entry] = None
+                    continue
+                store_cls = STORES.get(type(r))
+                if store_cls is None:
+                    raise CacheError(f"schedule entry {i}: no store is registered for cache requests of type "
+                                     f"{type(r).__name__} (registered: {sorted(c.__name__ for c in STORES)})")
+                single[entry] = r
+                key = store_cls.group_key(r)
+                if key is None:
+                    own.append((store_cls, r, [entry]))
+                else:
+                    shared.setdefault((store_cls, key), []).append(entry)
+        built = [(cls, single[entries[0]], entries) for (cls, _), entries in shared.items()] + own
+        order = lambda e: e if isinstance(e, tuple) else (e, -1)
+        for store_cls, rq, entries in sorted(built, key=lambda b: order(b[2][0])):
             st = store_cls(rq, entries, n_pages=self.n_pages, page_size=page_size, dtype=dtype,
                            device=self.device, max_slots=self.max_slots)
             self.stores.append(st)
@@ -345,10 +382,15 @@ class SequenceCache:
                 st.index = len(self.groups)
                 self.groups.append(st)
             for e in entries:
-                self._views[e] = st.view(e)
+                member_views[e] = st.view(e)
+        for e, v in member_views.items():
+            if not isinstance(e, tuple):
+                self._views[e] = v
+        for i, n in tuples.items():
+            self._views[i] = tuple(member_views[(i, k)] for k in range(n))
         # fixed-size states by schedule entry (kept for callers that look at them directly)
-        self.states: Dict[int, torch.Tensor] = {e: st.state for st in self.stores if isinstance(st, StateStore)
-                                                for e in st.entries}
+        self.states: Dict[object, torch.Tensor] = {e: st.state for st in self.stores if isinstance(st, StateStore)
+                                                   for e in st.entries}
         for i, src in enumerate(cache_of):
             if src is not None:
                 if self._views.get(src) is None:
@@ -467,6 +509,15 @@ class SequenceCache:
 
     def view(self, entry: int):
         return self._views[entry]
+
+    def save_states(self, slots: Sequence[int]) -> list:
+        """Everything a step folds tokens into for these slots (fixed-size states), for `load_states`."""
+        return [(st, st.save(slots)) for st in self.stores]
+
+    def load_states(self, saved: list) -> None:
+        for st, what in saved:
+            if what is not None:
+                st.load(what)
 
     def check(self) -> None:
         """Bookkeeping invariants (used by tests): nothing lost, nothing held twice."""

@@ -4,6 +4,7 @@ from .registry import (ConfigError, config_from_dict, load_config, register_arch
 from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule
 from .qwen3 import Qwen3Config
 from .gigopel import GigopelConfig
+from .sokirax import SokiraxConfig
 
 __all__ = ["ConfigError", "config_from_dict", "load_config", "register_architecture", "registered_architectures",
-           "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule", "Qwen3Config", "GigopelConfig"]
+           "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule", "Qwen3Config", "GigopelConfig", "SokiraxConfig"]

@@ -4,7 +4,10 @@
 // keys lo..p of that sequence (itself included: its key was written before this kernel runs),
 // lo = 0, or p - window + 1 for a windowed layer.  Query head h reads kv head h / (nq / nkv).
 // Scores, the running maximum, the exponentials, their sum and the weighted sum of values are
-// float32.  This is the 32-bit path and the twin the fast kernels are checked against; it
+// float32.  The values' head size dv may differ from the keys' d.  With `sink` (one float per query head), the
+// softmax's denominator also holds exp(sink[h]): a score without a key or a value, not scaled.  `out_scale`
+// multiplies the result (a mixer whose output is weighted takes the weight here, before any rounding).
+// This is the 32-bit path and the twin the fast kernels are checked against; it
 // restates ops.AttentionScoresInto (pkg/ops/attention.go:10-47) and replaces the reference's
 // attn_qk / softmax / attn_v PTX kernels (pkg/gpu/cuda/ptx.go:679-889), which the host loops
 // over heads.
@@ -18,19 +21,20 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     const T* q, const T* k_pool, const T* v_pool, T* __restrict__ out,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int page_size,
-    int nq, int nkv, int d, float scale, int window, const PageBounds pb) {
+    int nq, int nkv, int d, int dv, float scale, int window, const float* __restrict__ sink, float out_scale,
+    const PageBounds pb) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float sm[];
     float* qs = sm;                       // [d]
-    float* accs = sm + d;                 // [ATT_WARPS][d]
-    float* ml = accs + ATT_WARPS * d;     // [ATT_WARPS][2]
+    float* accs = sm + d;                 // [ATT_WARPS][dv]
+    float* ml = accs + ATT_WARPS * dv;    // [ATT_WARPS][2]
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* o = out + ((size_t)t * nq + h) * d;
+    T* o = out + ((size_t)t * nq + h) * dv;
     const int b = seq_of_token[t];
     if (b < 0) {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f<T>(0.f);
+        for (int i = threadIdx.x; i < dv; i += blockDim.x) o[i] = from_f<T>(0.f);
         return;
     }
     const int pos = positions[t];
@@ -48,9 +52,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
     const int* pt = page_table + (size_t)b * max_pages;
     for (int j = lo + warp; j <= pos; j += ATT_WARPS) {
         const int page = gg_page(pt, j / page_size, max_pages, pb, 41);
-        const size_t base = (((size_t)page * nkv + g) * page_size + (j % page_size)) * d;
-        const T* kp = k_pool + base;
-        const T* vp = v_pool + base;
+        const size_t base = ((size_t)page * nkv + g) * page_size + (j % page_size);
+        const T* kp = k_pool + base * d;
+        const T* vp = v_pool + base * dv;
         float dot = 0.f;
         for (int i = lane; i < d; i += 32) dot = fmaf(qs[i], to_f<T>(kp[i]), dot);
         dot = warp_sum(dot) * scale;
@@ -61,44 +65,46 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_plain_kernel(
 #pragma unroll
         for (int jj = 0; jj < ATT_MAXD / 32; ++jj) {
             const int i = lane + 32 * jj;
-            if (i < d) acc[jj] = acc[jj] * corr + p * to_f<T>(vp[i]);
+            if (i < dv) acc[jj] = acc[jj] * corr + p * to_f<T>(vp[i]);
         }
         m = mn;
     }
 #pragma unroll
     for (int jj = 0; jj < ATT_MAXD / 32; ++jj) {
         const int i = lane + 32 * jj;
-        if (i < d) accs[warp * d + i] = acc[jj];
+        if (i < dv) accs[warp * dv + i] = acc[jj];
     }
     if (lane == 0) { ml[warp * 2] = m; ml[warp * 2 + 1] = l; }
     __syncthreads();
-    float M = -INFINITY;
+    float M = sink != nullptr ? sink[h] : -INFINITY;
     for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, ml[w * 2]);
-    float L = 0.f;
+    float L = sink != nullptr ? expf(sink[h] - M) : 0.f;
     float f[ATT_WARPS];
-    for (int w = 0; w < ATT_WARPS; ++w) { f[w] = expf(ml[w * 2] - M); L += ml[w * 2 + 1] * f[w]; }
-    const float inv = 1.0f / L;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    for (int w = 0; w < ATT_WARPS; ++w) { f[w] = ml[w * 2] == -INFINITY ? 0.f : expf(ml[w * 2] - M); L += ml[w * 2 + 1] * f[w]; }
+    const float inv = out_scale / L;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float s = 0.f;
-        for (int w = 0; w < ATT_WARPS; ++w) s += accs[w * d + i] * f[w];
+        for (int w = 0; w < ATT_WARPS; ++w) s += accs[w * dv + i] * f[w];
         o[i] = from_f<T>(s * inv);
     }
 }
 
-// q[T, nq, d] and out[T, nq, d] in `dtype`; pools [page][nkv][page_size][d] in `dtype`, n_pages of them.
+// q[T, nq, d] and out[T, nq, dv] in `dtype`; pools k [page][nkv][page_size][d], v [page][nkv][page_size][dv] in
+// `dtype`, n_pages of them.  sink: null or one float per query head.
 // status (may be null): where the debug build records a page id or table index out of range (code 41).
 GG_API gg_attention_plain(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                           const int* positions, const int* seq_of_token, const int* page_table,
-                          int max_pages, int page_size, int n_pages, int ntok, int nq, int nkv, int d,
-                          float scale, int window, int* status, cudaStream_t stream) {
+                          int max_pages, int page_size, int n_pages, int ntok, int nq, int nkv, int d, int dv,
+                          float scale, int window, const float* sink, float out_scale, int* status,
+                          cudaStream_t stream) {
     if (ntok <= 0) return 0;
-    if (d <= 0 || d > ATT_MAXD || nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535 || page_size <= 0) return GG_ERR_ARG;
-    const size_t smem = ((size_t)(1 + ATT_WARPS) * d + 2 * ATT_WARPS) * sizeof(float);
+    if (d <= 0 || dv <= 0 || dv > ATT_MAXD || d > 4096 || nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535 || page_size <= 0) return GG_ERR_ARG;
+    const size_t smem = ((size_t)d + (size_t)ATT_WARPS * dv + 2 * ATT_WARPS) * sizeof(float);
     dim3 grid(ntok, nq);
     GG_DISPATCH_DTYPE(dtype, T,
         gg_launch(attention_plain_kernel<T>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 1, 
             (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, positions, seq_of_token, page_table,
-            max_pages, page_size, nq, nkv, d, scale, window, PageBounds{n_pages, status}));
+            max_pages, page_size, nq, nkv, d, dv, scale, window, sink, out_scale, PageBounds{n_pages, status}));
     return gg_last_error();
 }
 

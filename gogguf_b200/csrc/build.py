@@ -56,6 +56,7 @@ MODULES: Dict[str, str] = {
     "attention_plain": "attention_plain.cu",
     "latent_attention": "latent_attention.cu",
     "moe": "moe.cu",
+    "retention": "retention.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_fast": "attention_fast.cu",

@@ -174,9 +174,10 @@ GG_API gg_row_stats(const float* x, void* xhat, float* ssq, int T, int H, cudaSt
 
 // ----------------------------------------------------------------------------- rotary tables
 // cos/sin[t, i] of angle = pos[t] * inv_freq[i], computed in float64 (the reference computes
-// its tables in float64 too, pkg/ops/rope_tables.go:6-20) and stored as float32.
+// its tables in float64 too, pkg/ops/rope_tables.go:6-20) and stored as float32.  `mag` multiplies both
+// tables (encodings that lengthen the rotated pairs; 1 for a plain rotation).
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                   float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
+                                   float* __restrict__ cosv, float* __restrict__ sinv, int T, int half, double mag) {
     pdl_launch();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -186,15 +187,15 @@ __global__ void rope_tables_kernel(const int* __restrict__ positions, const doub
     if (p < 0) p = 0;
     double s, c;
     sincos((double)p * inv_freq[i], &s, &c);
-    cosv[idx] = (float)c;
-    sinv[idx] = (float)s;
+    cosv[idx] = (float)(c * mag);
+    sinv[idx] = (float)(s * mag);
 }
 
 GG_API gg_rope_tables(const int* positions, const double* inv_freq, float* cosv, float* sinv,
-                      int T, int half, cudaStream_t stream) {
+                      int T, int half, double mag, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return 0;
     const int n = T * half;
-    gg_launch(rope_tables_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, positions, inv_freq, cosv, sinv, T, half);
+    gg_launch(rope_tables_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, positions, inv_freq, cosv, sinv, T, half, mag);
     return gg_last_error();
 }
 
@@ -388,6 +389,128 @@ GG_API gg_qk_norm_rope_cache(const void* qkv, int dtype, void* q_out, const floa
         gg_launch(qk_norm_rope_cache_kernel<T>, dim3(grid), dim3(warps * 32), smem, stream, 1, 
             (const T*)qkv, (T*)q_out, qw, kw, eps, cosv, sinv, positions, seq_of_token, page_table, max_pages,
             page_size, (T*)k_pool, (T*)v_pool, ntok, nq, nkv, d, rot, PageBounds{n_pages, status}));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- q/k/v preparation, general form
+// One block per token of the fused projection output qkv[T, nq*d + nkv*d + nkv*dv] (q heads, k heads, v heads):
+//   norm_mode 0: no q/k norm; 1: every q and k head normed over its d elements with one weight of size d;
+//   2: q normed over all its nq*d elements at once with a weight of that size, k over its nkv*d alike;
+//   then the rotation of the pairs (i, i + rot/2) of the first `rot` elements of every q and k head;
+//   q to q_out[T, nq, d], k into the paged key pool [page][kv_head][page_size][d], v (untouched) into the paged
+//   value pool [page][kv_head][page_size][dv].  The key and value head sizes may differ.  All arithmetic float32.
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_prep_kernel(
+    const T* qkv, T* __restrict__ q_out,
+    const float* __restrict__ qw, const float* __restrict__ kw, float eps, int norm_mode,
+    const float* cosv, const float* sinv,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ page_table, int max_pages, int page_size,
+    T* __restrict__ k_pool, T* __restrict__ v_pool,
+    int nq, int nkv, int d, int dv, int rot, const PageBounds pb) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int t = blockIdx.x;
+    const int nqk = (nq + nkv) * d, row = nqk + nkv * dv;
+    float* buf = sm;                 // [nqk] q and k as float
+    float* hs = sm + nqk;            // [nq + nkv] one factor per head
+    float* red = hs + nq + nkv;      // [33]
+    const int b = seq_of_token[t];
+    const T* src = qkv + (size_t)t * row;
+    const bool write_kv = k_pool != nullptr && b >= 0;
+    for (int i = threadIdx.x; i < nqk; i += blockDim.x) buf[i] = to_f<T>(src[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    if (norm_mode == 1) {
+        for (int h = warp; h < nq + nkv; h += nwarps) {
+            float ss = 0.f;
+            for (int i = lane; i < d; i += 32) { const float v = buf[h * d + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) hs[h] = 1.0f / sqrtf(ss / (float)d + eps);
+        }
+    } else if (norm_mode == 2) {
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < nq * d; i += blockDim.x) { const float v = buf[i]; sq = fmaf(v, v, sq); }
+        for (int i = nq * d + threadIdx.x; i < nqk; i += blockDim.x) { const float v = buf[i]; sk = fmaf(v, v, sk); }
+        sq = block_sum(sq, red);
+        sk = block_sum(sk, red);
+        const float fq = 1.0f / sqrtf(sq / (float)(nq * d) + eps), fk = 1.0f / sqrtf(sk / (float)(nkv * d) + eps);
+        for (int h = threadIdx.x; h < nq + nkv; h += blockDim.x) hs[h] = h < nq ? fq : fk;
+    }
+    __syncthreads();
+    int page = -1, slot_in_page = 0;
+    if (write_kv) {
+        const int pos = positions[t];
+        page = gg_page_w(page_table + (size_t)b * max_pages, pos / page_size, max_pages, pb, 46);
+        slot_in_page = pos % page_size;
+    }
+    const int half = rot >> 1;
+    const float* c = cosv + (size_t)t * half;
+    const float* s = sinv + (size_t)t * half;
+    for (int idx = threadIdx.x; idx < nqk; idx += blockDim.x) {
+        const int h = idx / d, i = idx - h * d;
+        const bool is_q = h < nq;
+        if (!is_q && page < 0) continue;
+        const float* w = is_q ? qw : kw;
+        // weight index: per head (mode 1) or over the whole projection (mode 2)
+        const int wbase = norm_mode == 2 ? (is_q ? h * d : (h - nq) * d) : 0;
+        const float f = norm_mode ? hs[h] : 1.f;
+        auto val = [&](int j) { return buf[h * d + j] * f * (norm_mode ? w[wbase + j] : 1.f); };
+        float o;
+        if (i < half) o = val(i) * c[i] - val(i + half) * s[i];
+        else if (i < rot) o = val(i - half) * s[i - half] + val(i) * c[i - half];
+        else o = val(i);
+        if (is_q) q_out[(size_t)t * nq * d + idx] = from_f<T>(o);
+        else k_pool[(((size_t)page * nkv + (h - nq)) * page_size + slot_in_page) * d + i] = from_f<T>(o);
+    }
+    if (page >= 0) {
+        for (int idx = threadIdx.x; idx < nkv * dv; idx += blockDim.x) {
+            const int h = idx / dv, i = idx - h * dv;
+            v_pool[(((size_t)page * nkv + h) * page_size + slot_in_page) * dv + i] = src[nqk + idx];
+        }
+    }
+}
+
+GG_API gg_qkv_prep(const void* qkv, int dtype, void* q_out, const float* qw, const float* kw, float eps, int norm_mode,
+                   const float* cosv, const float* sinv, const int* positions, const int* seq_of_token,
+                   const int* page_table, int max_pages, int page_size, int n_pages, void* k_pool, void* v_pool,
+                   int ntok, int nq, int nkv, int d, int dv, int rot, int* status, cudaStream_t stream) {
+    if (ntok <= 0) return 0;
+    if (d <= 0 || dv <= 0 || rot < 0 || rot > d || (rot & 1) || nq <= 0 || nkv <= 0 || page_size <= 0 ||
+        norm_mode < 0 || norm_mode > 2 || (norm_mode && (qw == nullptr || kw == nullptr))) return GG_ERR_ARG;
+    const size_t smem = ((size_t)(nq + nkv) * d + nq + nkv + 33) * sizeof(float);
+    if (smem > 200 * 1024) return GG_ERR_ARG;
+    GG_DISPATCH_DTYPE(dtype, T,
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(qkv_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        gg_launch(qkv_prep_kernel<T>, dim3(ntok), dim3(256), smem, stream, 1,
+            (const T*)qkv, (T*)q_out, qw, kw, eps, norm_mode, cosv, sinv, positions, seq_of_token, page_table, max_pages,
+            page_size, (T*)k_pool, (T*)v_pool, nq, nkv, d, dv, rot, PageBounds{n_pages, status}));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- norm of a part's output, added
+// x[r, :] += y[r, :] / sqrt(mean(y[r, :]^2) + eps) * w: the norm that follows a part in a block with norms on
+// both sides of its parts, and the add into the residual stream, in one pass.  All float32; one block per row.
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float* y, const float* __restrict__ w,
+                                                          int H, float eps) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const float* yr = y + r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float f = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) x[r * H + i] += yr[i] * f * w[i];
+}
+
+GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0) return GG_ERR_ARG;
+    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), 0, stream, 1, x, y, w, H, eps);
     return gg_last_error();
 }
 

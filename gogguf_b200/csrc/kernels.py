@@ -79,13 +79,15 @@ def row_stats(x: torch.Tensor, xhat: torch.Tensor, ssq: torch.Tensor) -> None:
     kernel("elementwise", "gg_row_stats")(_p(x), _p(xhat), _p(ssq), T, H, _stream())
 
 
-def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                mag: float = 1.0) -> None:
+    """cos, sin [T, half] (float32) = mag * cos / sin of positions[t] * inv_freq[i], angles in float64."""
     _need(positions, torch.int32, "positions")
     _need(inv_freq, torch.float64, "inv_freq")
     _need(cos, torch.float32, "cos")
     _need(sin, torch.float32, "sin")
     T, half = positions.numel(), inv_freq.numel()
-    kernel("elementwise", "gg_rope_tables")(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, half, _stream())
+    kernel("elementwise", "gg_rope_tables")(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, half, float(mag), _stream())
 
 
 def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
@@ -101,6 +103,43 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optiona
         _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], page_size,
         k_pool.shape[0] if k_pool is not None else 0, _p(k_pool), _p(v_pool),
         n_tokens, nq, nkv, d, rot, _p(status_word(qkv.device)), _stream())
+
+
+def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+             eps: float, norm_mode: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+             seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int, k_pool: Optional[torch.Tensor],
+             v_pool: Optional[torch.Tensor], n_tokens: int, nq: int, nkv: int, d: int, dv: int, rot: int) -> None:
+    """The general q/k/v preparation: qkv [T, nq*d + nkv*d + nkv*dv]; norm_mode 0 none, 1 per head (weights of
+    size d), 2 over the whole q and the whole k projection (weights of size nq*d and nkv*d); rotation of the first
+    `rot` elements of each q and k head; q to q_out, k and v into the paged pools (head sizes d and dv)."""
+    if q_out.dtype != qkv.dtype or (k_pool is not None and (k_pool.dtype != qkv.dtype or v_pool.dtype != qkv.dtype)):
+        raise KernelError("qkv_prep: qkv, q_out and the cache must share one dtype")
+    if not qkv.is_contiguous() or qkv.shape[-1] != (nq + nkv) * d + nkv * dv:
+        raise KernelError("qkv_prep: qkv must be contiguous [T, nq*d + nkv*d + nkv*dv]")
+    if norm_mode:
+        want = (d, d) if norm_mode == 1 else (nq * d, nkv * d)
+        _need(q_weight, torch.float32, "q norm weight")
+        _need(k_weight, torch.float32, "k norm weight")
+        if (q_weight.numel(), k_weight.numel()) != want:
+            raise KernelError(f"qkv_prep: norm weights of {q_weight.numel()} and {k_weight.numel()} elements, "
+                              f"{want[0]} and {want[1]} expected")
+    from .tcgen05_gemm import status_word
+    kernel("elementwise", "gg_qkv_prep")(
+        _p(qkv), dtype_code(qkv.dtype), _p(q_out), _p(q_weight), _p(k_weight), float(eps), int(norm_mode), _p(cos),
+        _p(sin), _p(positions), _p(seq_of_token), _p(page_table), page_table.shape[-1], page_size,
+        k_pool.shape[0] if k_pool is not None else 0, _p(k_pool), _p(v_pool),
+        n_tokens, nq, nkv, d, dv, rot, _p(status_word(qkv.device)), _stream())
+
+
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32."""
+    _need(x, torch.float32, "x")
+    _need(y, torch.float32, "y")
+    _need(weight, torch.float32, "norm weight")
+    H = x.shape[-1]
+    if y.shape != x.shape or weight.numel() != H:
+        raise KernelError("rmsnorm_add: shapes disagree")
+    kernel("elementwise", "gg_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, float(eps), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:
@@ -158,14 +197,22 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
 # ------------------------------------------------------------------------------- attention
 def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor,
-                    page_size: int, n_tokens: int, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
+                    page_size: int, n_tokens: int, nq: int, nkv: int, d: int, scale: float, window: int,
+                    dv: Optional[int] = None, sink: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """Attention over the paged cache on the CUDA cores; `dv` is the values' head size (default d), `sink` one
+    float32 per query head that joins the softmax's denominator, `out_scale` a factor on the result."""
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
         raise KernelError("attention: q, cache and out must share one dtype")
+    dv = d if dv is None else int(dv)
+    if k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
+        raise KernelError("attention: the pools' head sizes disagree with d and dv")
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
     from .tcgen05_gemm import status_word
     kernel("attention_plain", "gg_attention_plain")(
         _p(q), _p(k_pool), _p(v_pool), _p(out), dtype_code(q.dtype), _p(positions), _p(seq_of_token),
-        _p(page_table), page_table.shape[-1], page_size, k_pool.shape[0], n_tokens, nq, nkv, d, float(scale),
-        int(window), _p(status_word(q.device)), _stream())
+        _p(page_table), page_table.shape[-1], page_size, k_pool.shape[0], n_tokens, nq, nkv, d, dv, float(scale),
+        int(window), _p(sink), float(out_scale), _p(status_word(q.device)), _stream())
 
 
 # ------------------------------------------------------------------------------- latent attention
@@ -214,6 +261,36 @@ def latent_attention_plain(qcat: torch.Tensor, pool: torch.Tensor, out: torch.Te
         pool.shape[0], n_tokens, heads, R, r, float(scale), int(window), _p(status_word(qcat.device)), _stream())
 
 
+# ------------------------------------------------------------------------------- retention
+def retention_chunk_takes(d: int, dv: int) -> bool:
+    """Does the chunked form hold a head of these sizes (state and chunk in one block's shared memory)?"""
+    rc, dvs = 32, dv + 1        # RET_RC and the padded row of csrc/retention.cu (the launcher checks again)
+    return (2 * rc * d + 2 * rc * dvs + rc * (rc + 1) + d * dvs + rc + 1) * 4 <= 200 * 1024
+
+
+def retention(qkvg: torch.Tensor, out: torch.Tensor, raw: Optional[torch.Tensor], state: torch.Tensor,
+              cos: torch.Tensor, sin: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+              seq_of_token: torch.Tensor, decay: torch.Tensor, n_tokens: int, n_seqs: int, heads: int, d: int, dv: int,
+              rot: int, key_scale: float, eps: float, out_scale: float, form: int) -> None:
+    """Retention over the step's tokens, sequence by sequence, from and into state [slots][heads][d][dv] (float32).
+    qkvg [T, 2*heads*d + 2*heads*dv]: q heads, k heads, v heads, gate; out [T, heads*dv] in the same dtype gets
+    o / rms(o) * silu(gate) * out_scale.  form 0: token by token; 1: in chunks (see csrc/retention.cu)."""
+    if qkvg.dtype != out.dtype or not qkvg.is_contiguous() or not out.is_contiguous():
+        raise KernelError("retention: qkvg and out must be contiguous and share one dtype")
+    if qkvg.shape[-1] != 2 * heads * (d + dv) or out.shape[-1] != heads * dv:
+        raise KernelError("retention: shapes disagree")
+    _need(state, torch.float32, "state")
+    _need(decay, torch.float32, "decay")
+    if tuple(state.shape[1:]) != (heads, d, dv) or decay.numel() != heads:
+        raise KernelError("retention: the state must be [slots, heads, d, dv] and decay one number per head")
+    if raw is not None:
+        _need(raw, torch.float32, "raw")
+    kernel("retention", "gg_retention")(
+        _p(qkvg), dtype_code(qkvg.dtype), qkvg.shape[-1], _p(out), _p(raw), _p(state), _p(cos), _p(sin),
+        _p(cu_seqlens), _p(slots), _p(seq_of_token), _p(decay), int(n_tokens), int(n_seqs), int(heads), int(d), int(dv),
+        int(rot), float(key_scale), float(eps), float(out_scale), int(form), _stream())
+
+
 # ------------------------------------------------------------------------------- routed experts
 def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_tokens: int) -> None:
     """z[t, e] = wr[e] . h[t], float32 sums on the CUDA cores (the router is never computed in reduced precision)."""
@@ -236,14 +313,15 @@ def moe_route(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, s
 
 
 def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
-                n_tokens: int, top: int, weight_on_input: bool, limit: float, slope: float, out_scale: float) -> None:
+                n_tokens: int, top: int, weight_on_input: bool, limit: float, slope: float, out_scale: float,
+                up_offset: float = 1.0) -> None:
     """y[t * top + k] = out_scale * act(Wg[e] x, Wu[e] x) for e = idx[t, k]; w_gu [E, 2, F, W]."""
     E, two, F, W = w_gu.shape
     if two != 2 or h.shape[-1] != W or not h.is_contiguous() or not w_gu.is_contiguous() or not y.is_contiguous():
         raise KernelError("moe_gate_up: shapes disagree")
     kernel("moe", "gg_moe_gate_up")(_p(h), dtype_code(h.dtype), _p(w_gu), dtype_code(w_gu.dtype), _p(idx), _p(wts),
                                      _p(y), dtype_code(y.dtype), n_tokens, W, F, int(top), int(weight_on_input),
-                                     float(limit), float(slope), float(out_scale), _stream())
+                                     float(limit), float(slope), float(up_offset), float(out_scale), _stream())
 
 
 def moe_down(y: torch.Tensor, w_d: torch.Tensor, idx: torch.Tensor, residual: torch.Tensor, n_tokens: int, top: int,
@@ -280,7 +358,7 @@ MOE_MMA_MAX_PAIRS = 8192      # the most (token, choice) pairs the mma.sync expe
 
 def moe_expert_mma(x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor, n_pairs: int, out: torch.Tensor, gated: bool,
                    limit: float = 0.0, slope: float = 1.0, out_scale: float = 1.0,
-                   wts: Optional[torch.Tensor] = None) -> None:
+                   wts: Optional[torch.Tensor] = None, up_offset: float = 1.0) -> None:
     """The experts' products on the tensor cores for up to 8,192 pairs, through the chosen index.  gated: x [P, K]
     against w [E, 2, N, K], out bfloat16 [P, N] = out_scale * act(gate, up) (* wts[p]); else w [E, N, K], out float32."""
     _need(x, torch.bfloat16, "x")
@@ -290,7 +368,7 @@ def moe_expert_mma(x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor, n_pairs:
     if x.shape[-1] != K or out.shape[-1] != N or (gated and (w.dim() != 4 or w.shape[1] != 2)):
         raise KernelError("moe_expert_mma: shapes disagree")
     kernel("moe", "gg_moe_expert_mma")(_p(x), _p(w), _p(idx), int(n_pairs), E, _p(out), N, K, int(gated), float(limit),
-                                        float(slope), float(out_scale), _p(wts), _stream())
+                                        float(slope), float(up_offset), float(out_scale), _p(wts), _stream())
 
 
 def wait_probe(limit_cycles: int, code: int, status: torch.Tensor) -> torch.Tensor:

@@ -8,7 +8,7 @@
 //             it sits on the output).
 //   down:     residual[t] += sum_k Wd[e(t, k)] y[t, k]  (k in order: the sum does not depend on the batch).
 //
-// act "clamped glu": g' = min(g, L), u' = clamp(u, -L, L), g' * sigmoid(slope g') * (u' + 1).
+// act "clamped glu": g' = min(g, L), u' = clamp(u, -L, L), g' * sigmoid(slope g') * (u' + up_offset); the plain gated unit silu(g) u is L = infinity, slope 1, offset 0.
 // Router scores, the choice, the weights and all sums are float32.
 #include "common.cuh"
 
@@ -110,10 +110,10 @@ GG_API gg_moe_route(const float* z, int T, int E, int top, int softmax, int reno
 }
 
 // ----------------------------------------------------------------------------- activation
-__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope) {
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope, float up_offset) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+    return g / (1.0f + expf(-slope * g)) * (u + up_offset);
 }
 
 // ----------------------------------------------------------------------------- gate and up through the index
@@ -122,7 +122,7 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TX* h, const TW* __restrict__ w_gu, const int* idx,
                                                           const float* wts, TY* y, int W, int F, int top,
-                                                          int weight_on_input, float limit, float slope, float out_scale) {
+                                                          int weight_on_input, float limit, float slope, float up_offset, float out_scale) {
     pdl_launch();
     pdl_wait();
     extern __shared__ float xs[];
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TX* h, const TW*
     g = warp_sum(g);
     u = warp_sum(u);
     if (lane == 0) {
-        float a = clamped_glu(g, u, limit, slope) * out_scale;
+        float a = clamped_glu(g, u, limit, slope, up_offset) * out_scale;
         if (!weight_on_input) a *= wt;
         y[(size_t)p * F + f] = from_f<TY>(a);
     }
@@ -155,13 +155,13 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TX* h, const TW*
 
 GG_API gg_moe_gate_up(const void* h, int h_dtype, const void* w_gu, int w_dtype, const int* idx, const float* wts,
                       void* y, int y_dtype, int T, int W, int F, int top, int weight_on_input, float limit,
-                      float slope, float out_scale, cudaStream_t stream) {
+                      float slope, float up_offset, float out_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 48 * 1024 || (F + 7) / 8 > 65535) return GG_ERR_ARG;
     dim3 grid(T * top, (F + 7) / 8);
     const size_t smem = (size_t)W * sizeof(float);
 #define GG_GU(TX, TW, TY) gg_launch(moe_gate_up_kernel<TX, TW, TY>, dim3(grid), dim3(256), smem, stream, 1, (const TX*)h, \
-        (const TW*)w_gu, idx, wts, (TY*)y, W, F, top, weight_on_input, limit, slope, out_scale)
+        (const TW*)w_gu, idx, wts, (TY*)y, W, F, top, weight_on_input, limit, slope, up_offset, out_scale)
     if (h_dtype == GG_F32 && w_dtype == GG_F32 && y_dtype == GG_F32) GG_GU(float, float, float);
     else if (h_dtype == GG_BF16 && w_dtype == GG_BF16 && y_dtype == GG_F32) GG_GU(bf16, bf16, float);
     else if (h_dtype == GG_BF16 && w_dtype == GG_BF16 && y_dtype == GG_BF16) GG_GU(bf16, bf16, bf16);
@@ -271,7 +271,7 @@ GG_API gg_moe_gather(const void* h, const float* wts, const int* place, void* xs
 
 // y[i, f] = out_scale * act(gu[i, f], gu[i, F + f]) (times the pair's weight if it sits on the output), rows in
 // sorted order; pair_of[i] is the pair at place i (only read when the weight is on the output).
-__global__ void moe_glu_rows_kernel(const bf16* gu, bf16* y, long long n, int F, float limit, float slope, float out_scale,
+__global__ void moe_glu_rows_kernel(const bf16* gu, bf16* y, long long n, int F, float limit, float slope, float up_offset, float out_scale,
                                     const float* wts, const int* pair_of) {
     pdl_launch();
     pdl_wait();
@@ -279,17 +279,17 @@ __global__ void moe_glu_rows_kernel(const bf16* gu, bf16* y, long long n, int F,
     if (i >= n) return;
     const long long row = i / F;
     const int f = (int)(i % F);
-    float a = clamped_glu(__bfloat162float(gu[row * 2 * F + f]), __bfloat162float(gu[row * 2 * F + F + f]), limit, slope) * out_scale;
+    float a = clamped_glu(__bfloat162float(gu[row * 2 * F + f]), __bfloat162float(gu[row * 2 * F + F + f]), limit, slope, up_offset) * out_scale;
     if (pair_of != nullptr) a *= wts[pair_of[row]];
     y[i] = __float2bfloat16_rn(a);
 }
 
-GG_API gg_moe_glu_rows(const void* gu, void* y, int P, int F, float limit, float slope, float out_scale,
+GG_API gg_moe_glu_rows(const void* gu, void* y, int P, int F, float limit, float slope, float up_offset, float out_scale,
                        const float* wts, const int* pair_of, cudaStream_t stream) {
     if (P <= 0) return 0;
     const long long n = (long long)P * F;
     gg_launch(moe_glu_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)y, n, F,
-              limit, slope, out_scale, wts, pair_of);
+              limit, slope, up_offset, out_scale, wts, pair_of);
     return gg_last_error();
 }
 
@@ -358,7 +358,7 @@ __device__ __forceinline__ void mx_ldsm(uint32_t* r, const void* p) {
 
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, const bf16* __restrict__ w, const int* idx, int P,
-                                                             void* out, int N, int K, float limit, float slope,
+                                                             void* out, int N, int K, float limit, float slope, float up_offset,
                                                              float out_scale, const float* wts) {
     pdl_launch();
     extern __shared__ __align__(16) unsigned char mx_raw[];
@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, cons
                     if (n >= N) continue;
                     if (GATED)
                         reinterpret_cast<bf16*>(out)[(size_t)p * N + n] =
-                            __float2bfloat16_rn(clamped_glu(ag[nt][2 * half + j], au[nt][2 * half + j], limit, slope) * f);
+                            __float2bfloat16_rn(clamped_glu(ag[nt][2 * half + j], au[nt][2 * half + j], limit, slope, up_offset) * f);
                     else
                         reinterpret_cast<float*>(out)[(size_t)p * N + n] = ag[nt][2 * half + j];
                 }
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(128) moe_expert_mma_kernel(const bf16* x, cons
 
 // gated != 0: x [P, K], w [E, 2, N, K], out bfloat16 [P, N]; else w [E, N, K], out float32 [P, N].  P <= 8,192 pairs.
 GG_API gg_moe_expert_mma(const void* x, const void* w, const int* idx, int P, int E, void* out, int N, int K, int gated,
-                         float limit, float slope, float out_scale, const float* wts, cudaStream_t stream) {
+                         float limit, float slope, float up_offset, float out_scale, const float* wts, cudaStream_t stream) {
     if (P <= 0) return 0;
     if (E <= 0 || N <= 0 || K <= 0 || (K % 8) || P > MX_MAXP || (N + 63) / 64 > 65535 ||
         (((uintptr_t)x | (uintptr_t)w) & 15))
@@ -483,7 +483,7 @@ GG_API gg_moe_expert_mma(const void* x, const void* w, const int* idx, int P, in
             set_g = true;
         }
         return gg_launch(moe_expert_mma_kernel<true>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)x, (const bf16*)w, idx, P,
-                         out, N, K, limit, slope, out_scale, wts);
+                         out, N, K, limit, slope, up_offset, out_scale, wts);
     }
     if (!set_p) {
         cudaError_t er = cudaFuncSetAttribute(moe_expert_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
@@ -491,5 +491,5 @@ GG_API gg_moe_expert_mma(const void* x, const void* w, const int* idx, int P, in
         set_p = true;
     }
     return gg_launch(moe_expert_mma_kernel<false>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)x, (const bf16*)w, idx, P,
-                     out, N, K, limit, slope, out_scale, wts);
+                     out, N, K, limit, slope, up_offset, out_scale, wts);
 }

@@ -75,11 +75,15 @@ class GraphStepper(Stepper):
             x = self.run_layers(ctx)
             return self.run_head(ctx, x, rows, bucket)
 
-        # warm-up on a side stream: allocates the workspace, sets kernel attributes, compiles what is missing
+        # warm-up on a side stream: allocates the workspace, sets kernel attributes, compiles what is missing.
+        # It runs the step for real, and the replay runs it again: keys and values land on the same rows twice,
+        # but a state that tokens are folded into would take the token twice, so such states are put back
         side = torch.cuda.Stream(device=dev_t)
         side.wait_stream(torch.cuda.current_stream(dev_t))
         with torch.cuda.stream(side):
+            saved = self.cache.save_states([e.slot for e in entries])
             run()
+            self.cache.load_states(saved)
         torch.cuda.current_stream(dev_t).wait_stream(side)
         torch.cuda.synchronize(dev_t)
         from ..csrc import build

@@ -97,6 +97,44 @@ class ParallelBlock:
             self._run("feed_forward", x, ctx, lambda dst: self.feed_forward.forward(h, dst, ctx))
 
 
+@register_arrangement("sandwich_norm")
+class SandwichNormBlock:
+    """A norm on either side of each part: x += post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x))).  The
+    feed-forward (with its two norms) may be absent.  A part's output is collected in a zeroed float32 buffer;
+    the norm after the part and the add into the residual stream are one kernel, all in float32.  The norms
+    after the parts must be of the form y / rms(y) * weight (they expose `weight` and `eps`)."""
+
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
+    optional_roles = ("feed_forward", "feed_forward_norm", "feed_forward_post_norm")
+
+    def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
+        self.parts = dict(parts)
+        self.rt = rt
+        self.mixer, self.mixer_norm, self.mixer_post = parts["mixer"], parts["mixer_norm"], parts["mixer_post_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.ff_norm, self.ff_post = parts.get("feed_forward_norm"), parts.get("feed_forward_post_norm")
+        if self.feed_forward is not None and (self.ff_norm is None or self.ff_post is None):
+            raise ValueError("sandwich_norm: a feed-forward needs feed_forward_norm and feed_forward_post_norm")
+        for post in (self.mixer_post, self.ff_post):
+            if post is not None and not getattr(post, "foldable", False):
+                raise ValueError("sandwich_norm: the norm after a part must be y / rms(y) * weight")
+
+    def _part(self, x: torch.Tensor, ctx: StepContext, pre, post, call) -> None:
+        h = ctx.ws.get("block_normed", tuple(x.shape), self.rt.dtype)
+        pre.forward(x, h)
+        y = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
+        y.zero_()
+        call(h, y)
+        K.rmsnorm_add(x, y, post.weight, post.eps)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache, writes_cache: bool) -> None:
+        self._part(x, ctx, self.mixer_norm, self.mixer_post,
+                   lambda h, y: self.mixer.forward(h, y, ctx, cache, writes_cache))
+        if self.feed_forward is not None:
+            self._part(x, ctx, self.ff_norm, self.ff_post, lambda h, y: self.feed_forward.forward(h, y, ctx))
+
+
 def _offer_norm(part, norm, rt: Runtime) -> bool:
     absorb = getattr(part, "absorb_norm", None)
     if absorb is None or not (rt.fast and rt.fold_norms and rt.dtype == torch.bfloat16):

@@ -32,12 +32,13 @@ class TokenEmbedding:
 @register_head("linear_head")
 class LinearHead:
     """logits = W h in float32; W is the embedding matrix when the spec says `tied_to`
-    (pkg/model/qwen3/model.go:578-610, pkg/model/qwen3/tensors.go:36-48)."""
+    (pkg/model/qwen3/model.go:578-610, pkg/model/qwen3/tensors.go:36-48).  ``tensor`` of the spec names the
+    stored matrix under the part's prefix (default "weight")."""
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl(shape=(spec["vocab_size"], spec["hidden_size"]),
-                                     optional=spec.get("tied_to") is not None)}
+        return {spec.get("tensor", "weight"): TensorDecl(shape=(spec["vocab_size"], spec["hidden_size"]),
+                                                         optional=spec.get("tied_to") is not None)}
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime,
                  tied: Optional[torch.Tensor] = None):
@@ -47,7 +48,7 @@ class LinearHead:
                 raise ValueError("head is tied but no embedding matrix was given")
             self.proj = Linear(tied, rt)
         else:
-            self.proj = Linear(weights["weight"], rt)
+            self.proj = Linear(weights[spec.get("tensor", "weight")], rt)
 
     def forward(self, h: torch.Tensor, logits: torch.Tensor, ctx: StepContext, m: Optional[int] = None) -> None:
         self.proj(h, logits, m=m, ws=ctx.ws)

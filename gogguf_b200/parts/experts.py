@@ -6,7 +6,10 @@ a_p = softplus(p), a_q = 1/2 + softplus(q); the stored tensor `act` holds (p, q)
 Routed experts (`routed_experts`): router logits W_r h in float32, scores by sigmoid (or softmax), the `top_k`
 largest chosen, weights the chosen scores (optionally renormalised), the weight applied to the expert's input
 or to its output.  An expert is a gated unit: y = act(Wg x, Wu x), out = Wd y, with
-act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
+act "clamped_glu": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + up_offset)
+(up_offset 1 unless given); act "silu_glu": silu(g) u, the same unit without a limit, with slope 1 and offset 0.
+`shared` (optional: intermediate_size, prefix, names) adds one dense gated unit that every token runs
+(the `swiglu` feed-forward under the given prefix), summed with the routed experts' output.
 The experts' matrices are reached through the chosen index with nothing read back: on the CUDA cores pair by pair
 (the 32-bit path, sizes the tensor-core forms do not take), or in bfloat16 on mma.sync, a CTA per expert and 64
 output rows with the expert's pairs as the operand (decode steps, short prompts).  Steps of many tokens in
@@ -23,7 +26,7 @@ from ..config.spec import PartSpec
 from ..csrc import kernels as K
 from ..weights.loader import TensorDecl
 from .base import Linear, Runtime, StepContext
-from .registry import register_feed_forward
+from .registry import FEED_FORWARDS, lookup, register_feed_forward
 
 
 SORTED_FORM_MIN_WORK = 1.5e9      # rows per expert x inner width x width from which prompts take the sorted form
@@ -90,7 +93,22 @@ class RoutedExperts:
             t[p + n["gate"]] = TensorDecl(shape=(i, h))
             t[p + n["up"]] = TensorDecl(shape=(i, h))
             t[p + n["down"]] = TensorDecl(shape=(h, i))
+        sh = cls._shared_spec(spec)
+        if sh is not None:
+            for local, decl in lookup(FEED_FORWARDS, sh.kind, "feed-forward").tensors(sh).items():
+                t[sh.prefix + local] = decl
         return t
+
+    @classmethod
+    def _shared_spec(cls, spec: PartSpec):
+        """The shared unit as a part spec of its own (prefix relative to this part), or None."""
+        sh = spec.get("shared")
+        if not sh:
+            return None
+        params = dict(hidden_size=spec["hidden_size"], intermediate_size=sh["intermediate_size"])
+        if sh.get("names"):
+            params["names"] = dict(sh["names"])
+        return PartSpec(kind=sh.get("kind", "swiglu"), prefix=sh.get("prefix", "shared."), params=params)
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.rt = rt
@@ -106,10 +124,15 @@ class RoutedExperts:
             raise ValueError(f"routed experts: weight_on must be 'input' or 'output', got {where!r}")
         self.on_input = where == "input"
         act = dict(spec.get("activation") or {})
-        if act.get("kind", "clamped_glu") != "clamped_glu":
-            raise ValueError(f"routed experts: unknown activation {act.get('kind')!r} (clamped_glu)")
-        self.limit = float(act.get("limit", float("inf")))
-        self.slope = float(act.get("slope", 1.0))
+        kind = act.get("kind", "clamped_glu")
+        if kind == "clamped_glu":
+            self.limit = float(act.get("limit", float("inf")))
+            self.slope = float(act.get("slope", 1.0))
+            self.up_offset = float(act.get("up_offset", 1.0))
+        elif kind == "silu_glu":
+            self.limit, self.slope, self.up_offset = float("inf"), 1.0, 0.0
+        else:
+            raise ValueError(f"routed experts: unknown activation {kind!r} (clamped_glu, silu_glu)")
         n = self._names(spec)
         self.router_w = rt.matrix(weights[n["router"]])
         gu: List[torch.Tensor] = []
@@ -126,6 +149,11 @@ class RoutedExperts:
         self.w_gu = torch.stack(gu, dim=0).contiguous()       # [E, 2, F, W]
         self.w_d = torch.stack(dn, dim=0).contiguous()        # [E, W, F]
         self.out_scale = 1.0
+        self.shared = None
+        sh = self._shared_spec(spec)
+        if sh is not None:
+            cls = lookup(FEED_FORWARDS, sh.kind, "feed-forward")
+            self.shared = cls(sh, {local: weights.pop(sh.prefix + local) for local in cls.tensors(sh)}, rt)
         self._grouped = None
         # rows on 16-byte boundaries: what the tensor-core forms (mma.sync for few pairs, tcgen05 for many) take
         self._mma = (rt.fast and rt.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16
@@ -135,7 +163,10 @@ class RoutedExperts:
             self._grouped = experts_grouped.try_make(self)
 
     def scale_output(self, mult: float) -> bool:
-        """The factor goes onto the experts' activations in float32 (the down projections are linear)."""
+        """The factor goes onto the experts' activations in float32 (the down projections are linear).  With a
+        shared unit the part does not take a factor: the block applies it to the sum."""
+        if self.shared is not None:
+            return False
         self.out_scale = float(mult)
         return True
 
@@ -149,6 +180,11 @@ class RoutedExperts:
         return idx, wts
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        if self.shared is not None:
+            self.shared.forward(h, residual, ctx)
+        self._routed(h, residual, ctx)
+
+    def _routed(self, h: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         T = ctx.n_tokens
         idx, wts = self.route(h, ctx)
         P = T * self.top
@@ -165,11 +201,12 @@ class RoutedExperts:
             K.moe_gather(h, wts, None, xs, P, self.top, self.on_input)
             yb = ctx.ws.get("moe_act_rows", (P, self.inter), torch.bfloat16)
             K.moe_expert_mma(xs, self.w_gu, idx, P, yb, True, self.limit, self.slope, self.out_scale,
-                             None if self.on_input else wts)
+                             None if self.on_input else wts, up_offset=self.up_offset)
             rows = ctx.ws.get("moe_rows_out", (P, self.hidden), torch.float32)
             K.moe_expert_mma(yb, self.w_d, idx, P, rows, False)
             K.moe_combine(rows, None, residual, T, self.top, ctx.seq_of_token)
             return
         y = ctx.ws.get("moe_act", (T * self.top, self.inter), torch.float32)
-        K.moe_gate_up(h, self.w_gu, idx, wts, y, T, self.top, self.on_input, self.limit, self.slope, self.out_scale)
+        K.moe_gate_up(h, self.w_gu, idx, wts, y, T, self.top, self.on_input, self.limit, self.slope, self.out_scale,
+                      up_offset=self.up_offset)
         K.moe_down(y, self.w_d, idx, residual, T, self.top, ctx.seq_of_token)

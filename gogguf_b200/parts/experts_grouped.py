@@ -53,7 +53,7 @@ class _Grouped:
             n = off[e + 1] - off[e]
             if n:
                 self.gate_up[e](xs[off[e]:off[e + 1]], gu[off[e]:off[e + 1]], m=n, ws=ws)
-        kernel("moe", "gg_moe_glu_rows")(gu.data_ptr(), y.data_ptr(), P, F, p.limit, p.slope, p.out_scale,
+        kernel("moe", "gg_moe_glu_rows")(gu.data_ptr(), y.data_ptr(), P, F, p.limit, p.slope, p.up_offset, p.out_scale,
                                          wts.data_ptr(), 0 if p.on_input else pair_of.data_ptr(), _s())
         for e in range(E):
             n = off[e + 1] - off[e]

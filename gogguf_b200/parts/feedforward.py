@@ -1,5 +1,6 @@
 """Dense SwiGLU feed-forward: down( silu(gate h) * (up h) ), no bias
-(pkg/model/qwen3/model.go:273-286, pkg/ops/inplace.go:14-19)."""
+(pkg/model/qwen3/model.go:273-286, pkg/ops/inplace.go:14-19).  ``names`` of the spec renames the three stored
+matrices (keys gate, up, down)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -16,18 +17,23 @@ from .registry import register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU:
     @classmethod
+    def _names(cls, spec: PartSpec) -> Dict[str, str]:
+        n = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+        n.update(spec.get("names") or {})
+        return n
+
+    @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
         h, i = spec["hidden_size"], spec["intermediate_size"]
-        return {
-            "gate_proj.weight": TensorDecl(shape=(i, h)),
-            "up_proj.weight": TensorDecl(shape=(i, h)),
-            "down_proj.weight": TensorDecl(shape=(h, i)),
-        }
+        n = cls._names(spec)
+        return {n["gate"]: TensorDecl(shape=(i, h)), n["up"]: TensorDecl(shape=(i, h)),
+                n["down"]: TensorDecl(shape=(h, i))}
 
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
-        g, u = rt.matrix(weights["gate_proj.weight"]), rt.matrix(weights["up_proj.weight"])
+        n = self._names(spec)
+        g, u = rt.matrix(weights[n["gate"]]), rt.matrix(weights[n["up"]])
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
         self.rt = rt
@@ -41,7 +47,7 @@ class SwiGLU:
         if self.fused is None:
             # gate rows first, then up rows: one product for both, then the activation kernel
             self.gate_up = Linear(torch.cat([g, u], dim=0), rt)
-        self.down = Linear(weights["down_proj.weight"], rt)
+        self.down = Linear(weights[n["down"]], rt)
 
     def absorb_norm(self, norm) -> bool:
         """Take the block's pre-norm into the gate/up projection; `forward` then gets RowStats as `h`."""
