@@ -293,12 +293,20 @@ template <int D> __device__ __forceinline__ bf16* sw(bf16* tile, int row, int ch
     return tile + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
+// A softmax sink: a number per query head that joins the denominator as exp(sink[h]) (no key, no value, not
+// scaled).  `l` is the sum of 2^(score - m) over the keys with m the maximum in use (in log2 units, -inf when no
+// key was seen); what comes back is the denominator with the sink's share.
+__device__ __forceinline__ float attn_sink_sum(float l, float m, const float* __restrict__ sink, int head) {
+    if (sink == nullptr || m == -INFINITY) return l;
+    return l + fast_exp2(sink[head] * 1.4426950408889634f - m);
+}
+
 template <int D>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* q, const bf16* k_pool, const bf16* v_pool, bf16* __restrict__ out,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int n_seqs, int nq, int nkv, float scale_log2, int window,
-    const PageBounds pb) {
+    const float* __restrict__ sink, float out_scale, const PageBounds pb) {
     pdl_wait();      // no early release of the next kernel: many waves of CTAs that exclude its CTAs from their SMs
     constexpr int CH = D / 8;        // 16-byte chunks per row
     constexpr int KS = D / 16;       // k-steps of Q.K^T
@@ -449,7 +457,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     for (int r = 0; r < 2; ++r) {
         const int row = qrow + g + 8 * r;
         if (row >= rows) continue;
-        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        const float lr = attn_sink_sum(l[r], m[r], sink, h);
+        const float inv = lr > 0.f ? out_scale / lr : 0.f;
         bf16* dst = out + ((size_t)(tok0 + row0 + row) * nq + h) * D;
 #pragma unroll
         for (int i = 0; i < NT; ++i)
@@ -482,7 +491,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
     const bf16* q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ page_table, int max_pages, int nq, int nkv, float scale_log2, int window, int nsplit,
-    int cluster_reduce, int early_release, int n_pages, int* __restrict__ status) {
+    int cluster_reduce, int early_release, const float* __restrict__ sink, float out_scale, int n_pages,
+    int* __restrict__ status) {
     // A grid that is resident as a whole lets the next kernel's CTAs in at once: they share the SMs' free
     // shared memory and start fetching weights.  A grid of several waves releases only after its pages (the
     // rule on dependent launches in common.cuh): until then its own waiting CTAs should get the SMs.
@@ -678,7 +688,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
         }
         const int head = kvh * G + r;
         if (nsplit == 1) {
-            out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            const float Ls = attn_sink_sum(L, M, sink, head);
+            out[((size_t)tok * nq + head) * D + c] = __float2bfloat16_rn(Ls > 0.f ? acc * out_scale / Ls : 0.f);
         } else if (cluster_reduce && G * D <= ATT_PUSH_MAX_OUT) {
             // straight into the shared memory of the CTA that merges this output (slices of 32 go round the
             // ranks), and this head's (max, sum) to every CTA: no load has to cross the cluster afterwards
@@ -720,7 +731,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
                     acc += recv_o[(k * rounds + round) * 32 + lane] * f;
                 }
             }
-            out[((size_t)tok * nq + kvh * G) * D + idx] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            const float Ls = attn_sink_sum(L, M, sink, kvh * G + r);
+            out[((size_t)tok * nq + kvh * G) * D + idx] = __float2bfloat16_rn(Ls > 0.f ? acc * out_scale / Ls : 0.f);
         }
     } else if (cluster_reduce) {
         // (more than 1,024 outputs per kv head do not fit the receive area: the owner pulls instead)
@@ -749,7 +761,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(
                     acc += as[k] * f;
                 }
             }
-            out[((size_t)tok * nq + kvh * G + r) * D + c] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            const float Ls = attn_sink_sum(L, M, sink, kvh * G + r);
+            out[((size_t)tok * nq + kvh * G + r) * D + c] = __float2bfloat16_rn(Ls > 0.f ? acc * out_scale / Ls : 0.f);
         }
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -796,8 +809,8 @@ int attn_max_cluster() {
 template <int D, int STAGES>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, float* part_o, float* part_ml,
                       const int* positions, const int* seq_of_token, const int* page_table, int max_pages, int ntok,
-                      int nq, int nkv, float scale_log2, int window, int splits, bool cluster, int n_pages, int* status,
-                      cudaStream_t stream) {
+                      int nq, int nkv, float scale_log2, int window, int splits, bool cluster, const float* sink,
+                      float out_scale, int n_pages, int* status, cudaStream_t stream) {
     constexpr int smem = decode_tma_smem<D, STAGES>();
     static bool configured = false;
     auto kern = attn_decode_tma_kernel<D, STAGES>;
@@ -819,7 +832,7 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
     const int early = (long long)ntok * nkv * splits <= places ? 1 : 0;
     return gg_launch(kern, grid, dim3(160), smem, stream, cl ? splits : 1, tk, tv, (const bf16*)q, (bf16*)out, part_o,
                      part_ml, positions, seq_of_token, page_table, max_pages, nq, nkv, scale_log2, window, splits, cl,
-                     early, n_pages, status);
+                     early, sink, out_scale, n_pages, status);
 }
 
 
@@ -845,7 +858,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
     const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int max_pages, int n_seqs,
-    int nq, int nkv, float scale_log2, int window, int n_pages, int* __restrict__ status) {
+    int nq, int nkv, float scale_log2, int window, const float* __restrict__ sink, float out_scale, int n_pages,
+    int* __restrict__ status) {
     constexpr int HALVES = D / 64;
     constexpr int QBOX = 128 * 64 * 2;              // [64 columns x 128 rows] box of Q: 16 KB
     constexpr int KBOX = 64 * 64 * 2;               // [64 columns x 64 rows] box of K or V: 8 KB
@@ -1091,7 +1105,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
         if (ok && ntiles > 1) ok = tma::mbar_wait(pv_done, (uint32_t)((ntiles - 2) & 1), abort_flag, status, 28);
         if (ok && tma::mbar_wait(pv_done, (uint32_t)((ntiles - 1) & 1), abort_flag, status, 28)) {
             tc5::fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float ls = attn_sink_sum(l, m_used, sink, h);
+            const float inv = ls > 0.f ? out_scale / ls : 0.f;
             bf16* dst = out + ((size_t)(tok0 + row0 + row) * nq + h) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -1173,7 +1188,7 @@ GG_API gg_attn_decode(const void* q, const void* k_pool, const void* v_pool, voi
 GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_seqlens,
                        const int* ctx_lens, const int* seq_of_token, const int* page_table, int max_pages,
                        int page_size, int n_pages, int n_seqs, int max_tiles, int nq, int nkv, int d, float scale,
-                       int window, int* status, cudaStream_t stream) {
+                       int window, const float* sink, float out_scale, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_tiles <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || (d != 64 && d != 128) || nq > 65535) return GG_ERR_ARG;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -1189,11 +1204,11 @@ GG_API gg_attn_prefill(const void* q, const void* k_pool, const void* v_pool, vo
         }
         gg_launch(attn_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                               cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
-                                                              nq, nkv, scale_log2, window, PageBounds{n_pages, status});
+                                                              nq, nkv, scale_log2, window, sink, out_scale, PageBounds{n_pages, status});
     } else {
         gg_launch(attn_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, 1, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                                                              cu_seqlens, ctx_lens, seq_of_token, page_table, max_pages, n_seqs,
-                                                             nq, nkv, scale_log2, window, PageBounds{n_pages, status});
+                                                             nq, nkv, scale_log2, window, sink, out_scale, PageBounds{n_pages, status});
     }
     return gg_last_error();
 }
@@ -1228,7 +1243,8 @@ GG_API gg_attn_decode_tma_splits(int ntok, int nkv, int max_ctx, int use_cluster
 GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o, float* part_ml,
                           const int* positions, const int* seq_of_token, const int* page_table, int max_pages,
                           int page_size, int n_pages, int ntok, int nq, int nkv, int d, float scale, int window,
-                          int splits, int use_cluster, int* status, cudaStream_t stream) {
+                          int splits, int use_cluster, const float* sink, float out_scale, int* status,
+                          cudaStream_t stream) {
     if (ntok <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || (d != 64 && d != 128) || splits < 1 ||
         nkv > 65535 || splits > 65535 || n_pages <= 0 || status == nullptr)
@@ -1236,6 +1252,8 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
     const bool cluster = use_cluster != 0;
     if (cluster && splits > attn_max_cluster()) return GG_ERR_ARG;
     if (splits > 1 && !cluster && (part_o == nullptr || part_ml == nullptr)) return GG_ERR_ARG;
+    // the form that merges its splits by a second kernel knows neither a sink nor a factor on the output
+    if (splits > 1 && !cluster && (sink != nullptr || out_scale != 1.0f)) return GG_ERR_ARG;
     if ((((uintptr_t)k_pool) & 15) || (((uintptr_t)v_pool) & 15)) return GG_ERR_ARG;
     CUtensorMap tk, tv;
     const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE;
@@ -1245,10 +1263,10 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
     const float scale_log2 = scale * 1.4426950408889634f;
     if (d == 128)
         rc = launch_decode_tma<128, 3>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                       nq, nkv, scale_log2, window, splits, cluster, n_pages, status, stream);
+                                       nq, nkv, scale_log2, window, splits, cluster, sink, out_scale, n_pages, status, stream);
     else
         rc = launch_decode_tma<64, 4>(tk, tv, q, out, part_o, part_ml, positions, seq_of_token, page_table, max_pages, ntok,
-                                      nq, nkv, scale_log2, window, splits, cluster, n_pages, status, stream);
+                                      nq, nkv, scale_log2, window, splits, cluster, sink, out_scale, n_pages, status, stream);
     if (rc != 0 || splits == 1 || cluster) return rc;
     if (d == 128) gg_launch(attn_combine_kernel<128>, dim3(ntok * nq), dim3(128), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
     else gg_launch(attn_combine_kernel<64>, dim3(ntok * nq), dim3(64), 0, stream, 1, part_o, part_ml, (bf16*)out, splits);
@@ -1261,7 +1279,8 @@ GG_API gg_attn_decode_tma(const void* q, const void* k_pool, const void* v_pool,
 GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_seqlens,
                           const int* ctx_lens, const int* seq_of_token, const int* page_table, int max_pages,
                           int page_size, int n_pages, int n_tokens, int n_seqs, int max_tiles, int nq, int nkv, int d,
-                          float scale, int window, int* status, cudaStream_t stream) {
+                          float scale, int window, const float* sink, float out_scale, int* status,
+                          cudaStream_t stream) {
     if (n_seqs <= 0 || max_tiles <= 0 || n_tokens <= 0) return 0;
     if (page_size != PAGE || nq <= 0 || nkv <= 0 || nq % nkv || (d != 64 && d != 128) || nq > 65535 || max_tiles > 65535 ||
         n_pages <= 0 || status == nullptr)
@@ -1284,7 +1303,8 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
             cfg = true;
         }
         return gg_launch(attn_prefill_tc_kernel<128>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
-                         ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
+                         ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, sink, out_scale, n_pages,
+                         status);
     }
     constexpr int smem = 16384 + 2 * 8192 + 2 * 8192 + 256;
     static bool cfg64 = false;
@@ -1294,7 +1314,8 @@ GG_API gg_attn_prefill_tc(const void* q, const void* k_pool, const void* v_pool,
         cfg64 = true;
     }
     return gg_launch(attn_prefill_tc_kernel<64>, grid, dim3(192), smem, stream, 1, tq, tk, tv, (bf16*)out, cu_seqlens,
-                     ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, n_pages, status);
+                     ctx_lens, seq_of_token, page_table, max_pages, n_seqs, nq, nkv, scale_log2, window, sink, out_scale,
+                     n_pages, status);
 }
 
 // 1 if this library was built with checked page tables (the debug build), else 0.

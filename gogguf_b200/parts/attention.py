@@ -85,12 +85,12 @@ class AttentionMixer:
         self.nkv = int(spec["num_kv_heads"])
         self.d = int(spec["head_dim"])
         self.dv = int(spec.get("value_dim") or self.d)
-        if self.dv > MAX_HEAD_DIM:
-            raise ValueError(f"attention: value_dim={self.dv} is not supported (at most {MAX_HEAD_DIM})")
         if self.nq % self.nkv:
             raise ValueError(f"attention: {self.nq} query heads are not a multiple of {self.nkv} kv heads")
         if self.d > MAX_HEAD_DIM or self.d % 2:
             raise ValueError(f"attention: head_dim={self.d} is not supported (even, at most {MAX_HEAD_DIM})")
+        if self.dv > MAX_HEAD_DIM:
+            raise ValueError(f"attention: value_dim={self.dv} is not supported (at most {MAX_HEAD_DIM})")
         self.window = int(spec.get("window") or 0)
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(self.d))
         self.eps = float(spec.get("qk_norm_eps", 0.0))
@@ -133,7 +133,7 @@ class AttentionMixer:
         return True
 
     def scale_output(self, mult: float) -> bool:
-        """A factor on this mixer's output: applied to the attention output in float32 by the plain kernel."""
+        """A factor on this mixer's output: the attention kernels apply it to their float32 result."""
         self.out_scale = float(mult)
         return True
 
@@ -167,8 +167,8 @@ class AttentionMixer:
                                  ctx.seq_of_token, table, cache.page_size,
                                  cache.k if writes_cache else None, cache.v if writes_cache else None,
                                  T, nq, nkv, d, self.rot)
-        if self._fast is not None and self.sink is None and self.out_scale == 1.0:
-            self._fast(q, cache.k, cache.v, o, ctx, table, cache.page_size)
+        if self._fast is not None:
+            self._fast(q, cache.k, cache.v, o, ctx, table, cache.page_size, sink=self.sink, out_scale=self.out_scale)
         else:
             K.attention_plain(q, cache.k, cache.v, o, ctx.positions, ctx.seq_of_token, table,
                               cache.page_size, T, nq, nkv, d, self.scale, self.window, dv=dv, sink=self.sink,

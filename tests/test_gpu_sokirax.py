@@ -238,6 +238,50 @@ def test_retention_mechanism_alone(dt, H, d, dv, rdims, decay):
         assert float(state[5].min()) == 9.0                           # a slot nobody named is untouched
 
 
+@pytest.mark.parametrize("d,nq,nkv,window", [(64, 8, 2, 90), (128, 4, 1, 150), (64, 4, 4, 0), (128, 16, 2, 65)])
+def test_tensor_core_attention_with_a_sink_and_a_factor(d, nq, nkv, window):
+    """The three tensor-core forms (long portions, short portions, decode steps) against the plain kernel on the same
+    bfloat16 cache, with a sink per head and a factor on the output; and a sink that matters: leaving it out moves
+    the result by far more than the tolerance."""
+    from gogguf_b200.csrc import fast_attention
+    from gogguf_b200.parts.base import Runtime, StepContext, Workspace
+    K = _K()
+    g = torch.Generator().manual_seed(d + nq)
+    run = fast_attention.try_make(nq, nkv, d, 0.11, window)
+    assert run is not None
+    rt = Runtime(dtype=torch.bfloat16, device=torch.device(DEV))
+    n_pages, lens = 24, [300, 75, 200]
+    kp = (torch.randn(n_pages, nkv, 64, d, generator=g)).to(torch.bfloat16).to(DEV)
+    vp = (torch.randn(n_pages, nkv, 64, d, generator=g)).to(torch.bfloat16).to(DEV)
+    table = torch.tensor([[3, 9, 1, 20, 7], [4, 11, 0, 0, 0], [5, 6, 8, 2, 0]], dtype=torch.int32, device=DEV)
+    sink = (4.0 + 2.0 * torch.randn(nq, generator=g)).float().to(DEV)      # about as heavy as fifty keys
+
+    def check(news):
+        """news[b]: how many of request b's last positions are this step's tokens."""
+        pos = torch.cat([torch.arange(L - c, L) for L, c in zip(lens, news)]).to(torch.int32).to(DEV)
+        sot = torch.cat([torch.full((c,), b) for b, c in enumerate(news)]).to(torch.int32).to(DEV)
+        T = int(pos.numel())
+        cu = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32, device=DEV)
+        ctx = StepContext(runtime=rt, ws=Workspace(rt.device), n_tokens=T, n_seqs=len(lens), tokens=None, positions=pos,
+                          seq_of_token=sot, cu_seqlens=cu, slots=None,
+                          ctx_lens=torch.tensor(lens, dtype=torch.int32, device=DEV), page_tables={}, max_new=max(news),
+                          max_ctx=max(lens), decode=all(c == 1 for c in news))
+        q = torch.randn(T, nq * d, generator=g).to(torch.bfloat16).to(DEV)
+        got = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
+        want = torch.empty_like(got)
+        bare = torch.empty_like(got)
+        run(q, kp, vp, got, ctx, table, 64, sink=sink, out_scale=1.3)
+        K.attention_plain(q, kp, vp, want, pos, sot, table, 64, T, nq, nkv, d, 0.11, window, sink=sink, out_scale=1.3)
+        K.attention_plain(q, kp, vp, bare, pos, sot, table, 64, T, nq, nkv, d, 0.11, window, out_scale=1.3)
+        assert rel_err(got, want) < 1.2e-2, (news, rel_err(got, want))
+        assert rel_err(bare, want) > 0.1
+
+    check([300, 75, 200])      # whole prompts: 128-query tiles on tcgen05
+    check([140, 33, 64])       # portions that go on from the cache
+    check([20, 3, 31])         # short portions: 64-query tiles
+    check([1, 1, 1])           # decode steps
+
+
 def test_norm_of_a_parts_output_added_to_the_stream():
     K = _K()
     g = torch.Generator().manual_seed(2)
