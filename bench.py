@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload] [--prefill-lengths 256,1024] [--decode-contexts 16384,32768]
-    python bench.py --compare gigopel [--compare-sizes 2k,4k]      (another workload, see the end of this text)
+    python bench.py --compare gigopel|sokirax [--compare-sizes 2k,4k]      (another workload, see the end of this text)
 
 A "step" is one decode step of a batch: every sequence goes on by one token, sampled greedily on the
 device.  The timed region is exactly K steps after W warm-up steps, timed with CUDA events on the
@@ -27,6 +27,11 @@ window, parallel blocks, xIELU or routed-expert feed-forwards) beside Qwen3 at e
 and feed-forward parameter count (Qwen3 with full attention), random weights: one prefill step of 2,048 tokens and decode steps at batch
 8 and 64 from 2,048-token contexts, for an all-dense and an all-experts Gigopel model per size.  It prints one JSON
 line {"compare": "gigopel", "sizes": {...}} and per-model lines on stderr.
+
+`--compare sokirax` does the same for the Sokirax design (norms on both sides of every part; windowed attention,
+or windowed attention with sinks beside retention; gated units or routed experts with a shared unit): an all-dense
+and an all-experts model per size, layers alternating between the two mixers, beside the same Qwen3.  It prints
+{"compare": "sokirax", "sizes": {...}}.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures of an earlier measurement on this pool.  The weights (16 GB) are far larger than
@@ -174,6 +179,36 @@ def gigopel_config(z, kind):
                 layers=[dict(type="latent_attention", mixer=mixer, mlp=mlp) for _ in range(z["layers"])])
 
 
+# the same widths, depths and head counts for Sokirax; retention heads of 128 x 128, windows as Gigopel's
+SOKIRAX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=8, window=1024, ret_heads=8, ff=8192, experts=16, top=2, expert_ff=1024,
+               shared_ff=1024, layers=8, vocab=65536),
+    "4k": dict(width=4096, heads=32, kv_heads=8, window=2048, ret_heads=16, ff=16384, experts=32, top=4, expert_ff=2048,
+               shared_ff=2048, layers=8, vocab=65536),
+}
+
+
+def sokirax_config(z, kind):
+    """Layers alternate: attention (head size 128, stretched rotation) and attention with sinks (head size 64) beside
+    retention (heads of 128 x 128, decays from 1 - 2^-5 to 1 - 2^-12)."""
+    import math
+    H, G, W = z["heads"], z["kv_heads"], z["width"]
+    a = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=z["window"]),
+             rot=dict(base=1000000.0, dims=64, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    left = dict(heads=H, kv_heads=G, dim=64, vdim=64, scale=0.125, mask=dict(size=z["window"]),
+                rot=dict(base=250000.0, dims=32))
+    R = z["ret_heads"]
+    right = dict(heads=R, dim=128, vdim=128, rot=dict(base=1000000.0, dims=32),
+                 decay=[1.0 - 2.0 ** (-5.0 - 7.0 * i / max(R - 1, 1)) for i in range(R)])
+    p = dict(left=left, right=right, left_scale=1.2, right_scale=1.1)
+    mlp = dict(kind="dense", ff=(2 * z["ff"] // 3) // 128 * 128) if kind == "dense" else dict(
+        kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]),
+        shared=dict(ff=z["shared_ff"]))
+    return dict(architecture="Sokirax", vocab=z["vocab"], width=W, norm=dict(eps=1e-6), initializer_range=0.02,
+                layers=[dict(type="attention", mixer=a, mlp=mlp) if i % 2 == 0 else dict(type="parallel", mixer=p, mlp=mlp)
+                        for i in range(z["layers"])])
+
+
 def qwen3_like(z):
     """Qwen3 at the same width, depth, head count and feed-forward parameter count (3 matrices instead of 2), with
     full attention (its cache of a 2,048-token context is read whole; Gigopel reads its window)."""
@@ -268,18 +303,47 @@ def compare_run(a):
         flops = z["layers"] * (2 * t * mats + 2 * 2 * qw * keys) + 2 * z["vocab"] * h
         return flops, z["layers"] * mats * 2 + z["vocab"] * h * 2
 
+    def sok_numbers(z, kind, t):
+        """The same two figures for a Sokirax model (per layer kind, half of the layers each), and the cache and
+        state bytes a decode step reads per sequence."""
+        W, H, G, R, win = z["width"], z["heads"], z["kv_heads"], z["ret_heads"], z["window"]
+        att = (H * 128 + 2 * G * 128) * W + W * H * 128
+        par = (H * 64 + 2 * G * 64) * W + W * H * 64 + 4 * R * 128 * W + W * R * 128
+        dense_ff = (2 * z["ff"] // 3) // 128 * 128
+        ff_active = 3 * W * dense_ff if kind == "dense" else (z["top"] * z["expert_ff"] + z["shared_ff"]) * 3 * W + z["experts"] * W
+        ff_read = 3 * W * dense_ff if kind == "dense" else (z["experts"] * z["expert_ff"] + z["shared_ff"]) * 3 * W
+        keys = sum(min(i + 1, win) for i in range(t))
+        half = z["layers"] // 2
+        attn = 2 * 2 * H * 128 * keys * half + (2 * 2 * H * 64 * keys + t * R * 2 * 2 * 128 * 128) * half
+        flops = 2 * t * (half * (att + par) + z["layers"] * ff_active) + attn + 2 * z["vocab"] * W
+        wbytes = (half * (att + par) + z["layers"] * ff_read) * 2 + z["vocab"] * W * 2
+        per_seq = half * (min(t, win) * 2 * G * (128 + 64) * 2 + 2 * R * 128 * 128 * 4)
+        return flops, wbytes, per_seq
+
     out = {}
     T = PROMPT_LEN
+    design = a.compare
     for name in [x for x in a.compare_sizes.split(",") if x.strip()]:
         z = GIGOPEL_SIZES[name]
-        arms = [("gigopel_dense", gigopel_config(z, "dense")), ("gigopel_experts", gigopel_config(z, "moe")),
-                ("qwen3_like", qwen3_like(z))]
+        if design == "sokirax":
+            zs = SOKIRAX_SIZES[name]
+            arms = [("sokirax_dense", sokirax_config(zs, "dense")), ("sokirax_experts", sokirax_config(zs, "moe")),
+                    ("qwen3_like", qwen3_like(z))]
+        else:
+            arms = [("gigopel_dense", gigopel_config(z, "dense")), ("gigopel_experts", gigopel_config(z, "moe")),
+                    ("qwen3_like", qwen3_like(z))]
         res = {}
         for arm, cd in arms:
             cfg = config_from_dict(cd)
             model = Model.random(cfg, seed=3, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
             torch.cuda.synchronize()
-            flops, wbytes = qwen_numbers(cd, z, T) if arm == "qwen3_like" else gig_numbers(z, "dense" if arm.endswith("dense") else "moe", T)
+            per_seq = 0
+            if arm == "qwen3_like":
+                flops, wbytes = qwen_numbers(cd, z, T)
+            elif design == "sokirax":
+                flops, wbytes, per_seq = sok_numbers(zs, "dense" if arm.endswith("dense") else "moe", T)
+            else:
+                flops, wbytes = gig_numbers(z, "dense" if arm.endswith("dense") else "moe", T)
             pms, launches = prefill_ms(model, T)
             r = {"params_b": round(cfg.parameter_count() / 1e9, 3), "prefill_ms": round(pms, 3),
                  "prefill_tok_s": round(T / (pms / 1e3)), "prefill_tflops": round(flops / (pms / 1e3) / 1e12, 1),
@@ -289,11 +353,13 @@ def compare_run(a):
                 dms, kernels = decode_ms(model, b, T, max(16, min(a.steps, 64)), max(a.warmup, 3))
                 # experts: a step reads at most batch * top experts' matrices, not all of them
                 rb = wbytes
-                if arm == "gigopel_experts":
+                if arm in ("gigopel_experts", "sokirax_experts"):
                     used = min(z["experts"], b * z["top"])
                     rb -= z["layers"] * (z["experts"] - used) * 3 * z["width"] * z["expert_ff"] * 2
                 if arm == "qwen3_like":
                     rb += b * T * 2 * z["layers"] * 8 * 128 * 2
+                elif design == "sokirax":
+                    rb += b * per_seq
                 else:
                     rb += b * min(T, z["window"]) * z["layers"] * (z["kv_rank"] + z["rot_dim"]) * 2
                 r[f"decode_b{b}_ms"] = round(dms, 4)
@@ -305,7 +371,7 @@ def compare_run(a):
             del model
             torch.cuda.empty_cache()
         out[name] = res
-    print(json.dumps({"compare": "gigopel", "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), seeded token ids",
+    print(json.dumps({"compare": design, "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), seeded token ids",
                       "prompt_len": T, "peaks": pk["source"], "sizes": out}))
     return 0
 
@@ -331,7 +397,7 @@ def main():
                     "decode_by_context)")
     ap.add_argument("--prefill-lengths", default="", help="comma separated prompt lengths: time one prefill step of each "
                     "(printed on stderr, added to the line as prefill_sweep)")
-    ap.add_argument("--compare", default="", choices=["", "gigopel"],
+    ap.add_argument("--compare", default="", choices=["", "gigopel", "sokirax"],
                     help="another workload: the named design beside Qwen3 at equal size (prefill and decode), see the top")
     ap.add_argument("--compare-sizes", default="2k,4k", help="which of the comparison's layer sizes to run")
     a = ap.parse_args()

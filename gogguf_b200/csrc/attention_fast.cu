@@ -881,9 +881,13 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
     uint64_t* v_full = bars + 5;                    // [3]
     uint64_t* v_empty = bars + 8;                   // [3]
     uint64_t* s_full = bars + 11;                   // [2]
-    uint64_t* p_ready = bars + 13;
-    uint64_t* pv_done = bars + 14;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    // p_ready takes turns between two barriers: a softmax warp may be a page ahead of another (the scores of page
+    // j + 1 are there before the softmax of page j is over), and with one barrier its arrival for page j + 1 would
+    // count as the late warp's arrival for page j: the P V of page j would start on a P that is not written yet,
+    // and a late warp that then waits for a P V which needs its own arrival would never leave
+    uint64_t* p_ready = bars + 13;                  // [2]
+    uint64_t* pv_done = bars + 15;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // no early release of the next kernel here: see the note on dependent launches in common.cuh
@@ -893,7 +897,8 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
         for (int i = 0; i < 2; ++i) { tma::mbar_init(&k_full[i], 1); tma::mbar_init(&k_empty[i], 1); }
         for (int i = 0; i < 3; ++i) { tma::mbar_init(&v_full[i], 1); tma::mbar_init(&v_empty[i], 1); }
         tma::mbar_init(&s_full[0], 1); tma::mbar_init(&s_full[1], 1); tma::mbar_init(pv_done, 1);
-        tma::mbar_init(p_ready, 4);           // one arrival per softmax warp
+        tma::mbar_init(&p_ready[0], 4);       // one arrival per softmax warp
+        tma::mbar_init(&p_ready[1], 4);
         *abort_flag = 0;
         tma::mbar_fence_init();
         tma::prefetch_map(&tmQ); tma::prefetch_map(&tmK); tma::prefetch_map(&tmV);
@@ -978,7 +983,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
                     ok = issue_scores(j + 1);
                     if (!ok) break;
                 }
-                ok = tma::mbar_wait(p_ready, (uint32_t)(j & 1), abort_flag, status, 25);
+                ok = tma::mbar_wait(&p_ready[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, status, 25);
                 if (!ok) break;
                 const int vs = j % VST;
                 ok = tma::mbar_wait(&v_full[vs], (uint32_t)((j / VST) & 1), abort_flag, status, 26);
@@ -1098,7 +1103,7 @@ __global__ void __launch_bounds__(192) attn_prefill_tc_kernel(
             tc5::wait_st();
             tc5::fence_before();
             __syncwarp();
-            if (lane == 0) tma::mbar_arrive(p_ready);
+            if (lane == 0) tma::mbar_arrive(&p_ready[j & 1]);
         }
         // The last P V.  The scores of the last page say that the P V of two pages before is complete; the one
         // in between has not been waited for, and a wait by parity can only tell neighbouring phases apart.
