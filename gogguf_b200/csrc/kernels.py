@@ -291,6 +291,38 @@ def retention(qkvg: torch.Tensor, out: torch.Tensor, raw: Optional[torch.Tensor]
         int(rot), float(key_scale), float(eps), float(out_scale), int(form), _stream())
 
 
+RETENTION_CHUNK = 64          # tokens per chunk of the many-CTA form (RET_PC in csrc/retention.cu)
+RETENTION_CHUNKS_MAX_HEAD = 128
+
+
+def retention_chunks_scratch(n_tokens: int, n_seqs: int, heads: int, d: int, dv: int) -> int:
+    """Floats of scratch `retention_chunks` needs: a state per chunk and head."""
+    return (n_tokens // RETENTION_CHUNK + n_seqs) * heads * d * dv
+
+
+def retention_chunks(qkvg: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, state: torch.Tensor,
+                     cos: torch.Tensor, sin: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+                     seq_of_token: torch.Tensor, decay: torch.Tensor, n_tokens: int, n_seqs: int, heads: int, d: int,
+                     dv: int, rot: int, key_scale: float, eps: float, out_scale: float) -> None:
+    """`retention` for prompts, cut so that every chunk of 64 tokens of every head is a CTA of its own: what each
+    chunk adds to the state, a walk over the chunks' states, the outputs chunk by chunk (head sizes up to 128)."""
+    if qkvg.dtype != out.dtype or not qkvg.is_contiguous() or not out.is_contiguous():
+        raise KernelError("retention: qkvg and out must be contiguous and share one dtype")
+    if qkvg.shape[-1] != 2 * heads * (d + dv) or out.shape[-1] != heads * dv:
+        raise KernelError("retention: shapes disagree")
+    _need(state, torch.float32, "state")
+    _need(decay, torch.float32, "decay")
+    _need(scratch, torch.float32, "scratch")
+    if tuple(state.shape[1:]) != (heads, d, dv) or decay.numel() != heads:
+        raise KernelError("retention: the state must be [slots, heads, d, dv] and decay one number per head")
+    if scratch.numel() < retention_chunks_scratch(n_tokens, n_seqs, heads, d, dv):
+        raise KernelError("retention: the scratch is too small")
+    kernel("retention", "gg_retention_chunks")(
+        _p(qkvg), dtype_code(qkvg.dtype), qkvg.shape[-1], _p(out), _p(scratch), _p(state), _p(cos), _p(sin),
+        _p(cu_seqlens), _p(slots), _p(seq_of_token), _p(decay), int(n_tokens), int(n_seqs), int(heads), int(d), int(dv),
+        int(rot), float(key_scale), float(eps), float(out_scale), _stream())
+
+
 # ------------------------------------------------------------------------------- routed experts
 def moe_router_logits(h: torch.Tensor, wr: torch.Tensor, z: torch.Tensor, n_tokens: int) -> None:
     """z[t, e] = wr[e] . h[t], float32 sums on the CUDA cores (the router is never computed in reduced precision)."""

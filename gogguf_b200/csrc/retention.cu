@@ -8,7 +8,7 @@
 // the root, no weight), multiplied by silu(g_t) and by `out_scale`, and stored in the compute dtype for the
 // output projection.  Everything between the projections' outputs and that store is float32.
 //
-// Two forms of the same sums:
+// Three forms of the same sums (the third, over many CTAs, is described further down):
 //   * scan: tokens one after the other, the state in registers (a thread owns one column of the state and up to
 //     RPT of its rows).  Decode steps, the 32-bit path, and the twin of the chunked form.
 //   * chunked: a prompt's tokens in chunks of RC; inside a chunk the outputs are
@@ -313,5 +313,292 @@ GG_API gg_retention(const void* qkvg, int dtype, int ld, void* out, float* raw, 
     GG_DISPATCH_DTYPE(dtype, T,
         gg_launch(retention_gate_kernel<T>, dim3((unsigned)((total + 3) / 4)), dim3(128), 0, stream, 1,
                   (const float*)raw, (const T*)qkvg, ld, (T*)out, seq_of_token, ntok, H, d, dv, eps, out_scale));
+    return gg_last_error();
+}
+
+// ----------------------------------------------------------------------------- chunked form over many CTAs
+// The same sums as the chunked form above, cut so that every chunk of every head is a CTA of its own:
+//   1. ret_chunk_state_kernel (one CTA per chunk and head): U_c = sum_j decay^(n-1-j) k_j v_j^T, what the chunk
+//      adds to the state, into scratch [chunk][head][d][dv];
+//   2. ret_chunk_scan_kernel (one thread per state element): walks a sequence's chunks, S_in(c+1) = decay^n S_in(c)
+//      + U_c from the slot's state, leaves S_in(c) in U_c's place and the last state in the slot;
+//   3. ret_chunk_out_kernel (one CTA per chunk and head): o_i = decay^(i+1) q_i^T S_in(c) + sum_{j<=i} decay^(i-j)
+//      (q_i . k_j) v_j, then norm, gate and store.
+// float32 on the CUDA cores; 16 x 16 threads with register tiles; head sizes up to 128 x 128.
+#define RET_PC 64            // tokens per chunk
+#define RET_PMAX 128         // largest d and dv
+
+// Which (sequence, chunk) is CTA `item`?  Chunks are numbered sequence after sequence, padding rows have none.
+__device__ __forceinline__ bool ret_find_chunk(int item, const int* cu_seqlens, const int* seq_of_token, int n_seqs,
+                                               int& b, int& t0, int& n) {
+    for (int i = 0; i < n_seqs; ++i) {
+        const int a = cu_seqlens[i], e = cu_seqlens[i + 1];
+        if (e <= a || seq_of_token[a] < 0) continue;
+        const int nc = (e - a + RET_PC - 1) / RET_PC;
+        if (item < nc) { b = i; t0 = a + item * RET_PC; n = min(RET_PC, e - t0); return true; }
+        item -= nc;
+    }
+    return false;
+}
+
+// Rotated q (optional) and k of `n` tokens from row t0 into shared memory with row stride ds, k times kscale and
+// times wk[j] (a weight per token); v with row stride dv.
+template <typename T>
+__device__ __forceinline__ void ret_stage(const T* qkvg, int ld, int t0, int n, int h, int H, int d, int dv, int rot,
+                                          float kscale, const float* cosv, const float* sinv, float* qs, float* ks,
+                                          float* vs, int ds, const float* wk) {
+    const int half = rot >> 1;
+    for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
+        const int tt = idx / d, i = idx - tt * d;
+        const T* row = qkvg + (size_t)(t0 + tt) * ld;
+        const T* qp = row + h * d;
+        const T* kp = row + (size_t)H * d + h * d;
+        float qv = 0.f, kv;
+        if (i < rot) {
+            const float* c = cosv + (size_t)(t0 + tt) * half;
+            const float* s = sinv + (size_t)(t0 + tt) * half;
+            if (i < half) {
+                if (qs) qv = to_f<T>(qp[i]) * c[i] - to_f<T>(qp[i + half]) * s[i];
+                kv = to_f<T>(kp[i]) * c[i] - to_f<T>(kp[i + half]) * s[i];
+            } else {
+                const int p = i - half;
+                if (qs) qv = to_f<T>(qp[p]) * s[p] + to_f<T>(qp[i]) * c[p];
+                kv = to_f<T>(kp[p]) * s[p] + to_f<T>(kp[i]) * c[p];
+            }
+        } else {
+            if (qs) qv = to_f<T>(qp[i]);
+            kv = to_f<T>(kp[i]);
+        }
+        if (qs) qs[tt * ds + i] = qv;
+        ks[tt * ds + i] = kv * kscale * (wk ? wk[tt] : 1.f);
+    }
+    for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
+        const int tt = idx / dv, j = idx - tt * dv;
+        vs[tt * dv + j] = to_f<T>(qkvg[(size_t)(t0 + tt) * ld + (size_t)2 * H * d + h * dv + j]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ret_chunk_state_kernel(
+    const T* qkvg, int ld, float* U, const float* cosv, const float* sinv, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ seq_of_token, const float* __restrict__ decay, int n_seqs, int H, int d, int dv, int rot,
+    float kscale) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    int b, t0, n;
+    if (!ret_find_chunk(blockIdx.x, cu_seqlens, seq_of_token, n_seqs, b, t0, n)) return;
+    const int h = blockIdx.y, ds = d + 1;
+    float* ks = sm;                        // [PC][ds], already times decay^(n-1-j)
+    float* vs = ks + RET_PC * ds;          // [PC][dv]
+    float* wk = vs + RET_PC * dv;          // [PC]
+    const float a = decay[h];
+    if (threadIdx.x < n) {
+        float p = 1.f;
+        for (int i = 0; i < n - 1 - (int)threadIdx.x; ++i) p *= a;
+        wk[threadIdx.x] = p;
+    }
+    __syncthreads();
+    ret_stage<T>(qkvg, ld, t0, n, h, H, d, dv, rot, kscale, cosv, sinv, nullptr, ks, vs, ds, wk);
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[RET_PMAX / 16][RET_PMAX / 16];
+#pragma unroll
+    for (int i = 0; i < RET_PMAX / 16; ++i)
+#pragma unroll
+        for (int j = 0; j < RET_PMAX / 16; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        float kr[RET_PMAX / 16], vc[RET_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < RET_PMAX / 16; ++i) {
+            kr[i] = ty + 16 * i < d ? ks[j * ds + ty + 16 * i] : 0.f;
+            vc[i] = tx + 16 * i < dv ? vs[j * dv + tx + 16 * i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < RET_PMAX / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < RET_PMAX / 16; ++c) acc[i][c] = fmaf(kr[i], vc[c], acc[i][c]);
+    }
+    float* up = U + ((size_t)blockIdx.x * H + h) * d * dv;
+#pragma unroll
+    for (int i = 0; i < RET_PMAX / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c)
+            if (ty + 16 * i < d && tx + 16 * c < dv) up[(size_t)(ty + 16 * i) * dv + tx + 16 * c] = acc[i][c];
+}
+
+__global__ void __launch_bounds__(256) ret_chunk_scan_kernel(
+    float* U, float* state, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+    const int* __restrict__ seq_of_token, const float* __restrict__ decay, int H, int d, int dv) {
+    pdl_launch();
+    pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
+    if (e >= d * dv || end <= start || seq_of_token[start] < 0) return;
+    int base = 0;
+    for (int i = 0; i < b; ++i) {
+        const int a0 = cu_seqlens[i], e0 = cu_seqlens[i + 1];
+        if (e0 > a0 && seq_of_token[a0] >= 0) base += (e0 - a0 + RET_PC - 1) / RET_PC;
+    }
+    const int n_new = end - start, nch = (n_new + RET_PC - 1) / RET_PC;
+    const float a = decay[h];
+    float aC = 1.f;
+    for (int i = 0; i < RET_PC; ++i) aC *= a;
+    float* sp = state + (((size_t)slots[b] * H + h) * d) * dv + e;
+    float s = *sp;
+    for (int c = 0; c < nch; ++c) {
+        float* up = U + ((size_t)(base + c) * H + h) * d * dv + e;
+        const float u = *up;
+        *up = s;                           // the state the chunk starts from
+        const int n = min(RET_PC, n_new - c * RET_PC);
+        float an = aC;
+        if (n < RET_PC) { an = 1.f; for (int i = 0; i < n; ++i) an *= a; }
+        s = fmaf(s, an, u);
+    }
+    *sp = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ret_chunk_out_kernel(
+    const T* qkvg, int ld, T* out, const float* Sin, const float* cosv, const float* sinv,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token, const float* __restrict__ decay,
+    int n_seqs, int H, int d, int dv, int rot, float kscale, float eps, float out_scale) {
+    pdl_launch();
+    pdl_wait();
+    extern __shared__ float sm[];
+    int b, t0, n;
+    if (!ret_find_chunk(blockIdx.x, cu_seqlens, seq_of_token, n_seqs, b, t0, n)) return;
+    const int h = blockIdx.y, ds = d + 1, wide = max(ds, dv);
+    float* qs = sm;                           // [PC][wide]: q rows (stride ds), later the raw outputs (stride dv)
+    float* ks = qs + RET_PC * wide;           // [PC][ds]
+    float* vs = ks + RET_PC * ds;             // [PC][dv]
+    float* A = vs + RET_PC * dv;              // [PC][PC + 1]
+    float* pw = A + RET_PC * (RET_PC + 1);    // [PC + 1]
+    const float a = decay[h];
+    if (threadIdx.x <= RET_PC) {
+        float p = 1.f;
+        for (int i = 0; i < (int)threadIdx.x; ++i) p *= a;
+        pw[threadIdx.x] = p;
+    }
+    ret_stage<T>(qkvg, ld, t0, n, h, H, d, dv, rot, kscale, cosv, sinv, qs, ks, vs, ds, nullptr);
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    {   // A[i][j] = decay^(i-j) (q_i . k_j) for j <= i < n, else 0
+        float acc[RET_PC / 16][RET_PC / 16];
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+            for (int j = 0; j < RET_PC / 16; ++j) acc[i][j] = 0.f;
+        for (int r = 0; r < d; ++r) {
+            float qv[RET_PC / 16], kv[RET_PC / 16];
+#pragma unroll
+            for (int i = 0; i < RET_PC / 16; ++i) {
+                qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * ds + r] : 0.f;
+                kv[i] = tx + 16 * i < n ? ks[(tx + 16 * i) * ds + r] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+                for (int j = 0; j < RET_PC / 16; ++j) acc[i][j] = fmaf(qv[i], kv[j], acc[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+            for (int j = 0; j < RET_PC / 16; ++j) {
+                const int qi = ty + 16 * i, kj = tx + 16 * j;
+                A[qi * (RET_PC + 1) + kj] = (kj <= qi && qi < n) ? acc[i][j] * pw[qi - kj] : 0.f;
+            }
+    }
+    // o[i][c]: rows i = ty + 16 a, columns c = tx + 16 b
+    float o[RET_PC / 16][RET_PMAX / 16];
+#pragma unroll
+    for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] = 0.f;
+    const float* S = Sin + ((size_t)blockIdx.x * H + h) * d * dv;
+    for (int r = 0; r < d; ++r) {
+        float qv[RET_PC / 16], sv[RET_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i) qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * ds + r] : 0.f;
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c) sv[c] = tx + 16 * c < dv ? S[(size_t)r * dv + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] = fmaf(qv[i], sv[c], o[i][c]);
+    }
+#pragma unroll
+    for (int i = 0; i < RET_PC / 16; ++i) {
+        const float f = pw[min(ty + 16 * i + 1, RET_PC)];
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] *= f;
+    }
+    __syncthreads();                          // A is whole; every thread is done with the q rows
+    for (int j = 0; j < n; ++j) {
+        float av[RET_PC / 16], vv[RET_PMAX / 16];
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i) av[i] = A[(ty + 16 * i) * (RET_PC + 1) + j];
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c) vv[c] = tx + 16 * c < dv ? vs[j * dv + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+            for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] = fmaf(av[i], vv[c], o[i][c]);
+    }
+    float* os = qs;                           // raw outputs [PC][dv]
+#pragma unroll
+    for (int i = 0; i < RET_PC / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < RET_PMAX / 16; ++c)
+            if (ty + 16 * i < n && tx + 16 * c < dv) os[(ty + 16 * i) * dv + tx + 16 * c] = o[i][c];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = warp; i < n; i += 8) {
+        float ss = 0.f;
+        for (int c = lane; c < dv; c += 32) ss = fmaf(os[i * dv + c], os[i * dv + c], ss);
+        ss = warp_sum(ss);
+        const float f = out_scale / sqrtf(ss / (float)dv + eps);
+        const T* gp = qkvg + (size_t)(t0 + i) * ld + (size_t)2 * H * d + (size_t)H * dv + h * dv;
+        T* op = out + (size_t)(t0 + i) * H * dv + h * dv;
+        for (int c = lane; c < dv; c += 32) op[c] = from_f<T>(os[i * dv + c] * f * silu_f(to_f<T>(gp[c])));
+    }
+}
+
+// Zero rows for the padding sequences of a replayed batch (the chunk kernels skip them).
+template <typename T>
+__global__ void ret_zero_padding_kernel(T* out, const int* __restrict__ seq_of_token, int ntok, int width) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (t >= ntok || seq_of_token[t] >= 0) return;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * width + c] = from_f<T>(0.f);
+}
+
+// The many-CTA chunked form.  scratch: (ntok / 64 + n_seqs) * H * d * dv floats (a state per chunk and head).
+// d, dv <= 128.
+GG_API gg_retention_chunks(const void* qkvg, int dtype, int ld, void* out, float* scratch, float* state, const float* cosv,
+                           const float* sinv, const int* cu_seqlens, const int* slots, const int* seq_of_token,
+                           const float* decay, int ntok, int n_seqs, int H, int d, int dv, int rot, float kscale, float eps,
+                           float out_scale, cudaStream_t stream) {
+    if (ntok <= 0 || n_seqs <= 0) return 0;
+    if (H <= 0 || H > 65535 || d <= 0 || dv <= 0 || d > RET_PMAX || dv > RET_PMAX || rot < 0 || rot > d || (rot & 1) ||
+        scratch == nullptr) return GG_ERR_ARG;
+    const int chunks = ntok / RET_PC + n_seqs, ds = d + 1, wide = ds > dv ? ds : dv;
+    const size_t smem_a = ((size_t)RET_PC * (ds + dv + 1)) * sizeof(float);
+    const size_t smem_c = ((size_t)RET_PC * (wide + ds + dv + RET_PC + 1) + RET_PC + 1) * sizeof(float);
+    GG_DISPATCH_DTYPE(dtype, T,
+        if (smem_a > 48 * 1024)
+            cudaFuncSetAttribute(ret_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        if (smem_c > 48 * 1024)
+            cudaFuncSetAttribute(ret_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
+        gg_launch(ret_chunk_state_kernel<T>, dim3(chunks, H), dim3(256), smem_a, stream, 1, (const T*)qkvg, ld, scratch,
+                  cosv, sinv, cu_seqlens, seq_of_token, decay, n_seqs, H, d, dv, rot, kscale);
+        gg_launch(ret_chunk_scan_kernel, dim3(n_seqs, H, (d * dv + 255) / 256), dim3(256), 0, stream, 1, scratch, state,
+                  cu_seqlens, slots, seq_of_token, decay, H, d, dv);
+        gg_launch(ret_chunk_out_kernel<T>, dim3(chunks, H), dim3(256), smem_c, stream, 1, (const T*)qkvg, ld, (T*)out,
+                  (const float*)scratch, cosv, sinv, cu_seqlens, seq_of_token, decay, n_seqs, H, d, dv, rot, kscale, eps,
+                  out_scale);
+        gg_launch(ret_zero_padding_kernel<T>, dim3(ntok), dim3(128), 0, stream, 1, (T*)out, seq_of_token, ntok, H * dv));
     return gg_last_error();
 }

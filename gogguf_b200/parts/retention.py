@@ -80,8 +80,11 @@ class RetentionMixer:
         self.qkvg = Linear(torch.cat(mats, dim=0), rt)
         self.o = Linear(weights[n["o"]], rt)
         self.out_scale = 1.0
-        self._chunked = (K.retention_chunk_takes(self.d, self.dv)
-                         and os.environ.get("GOGGUF_B200_RETENTION_CHUNKED", "1") != "0")
+        # prompts: chunks over many CTAs where the head sizes allow (GOGGUF_B200_RETENTION_CHUNKED=1: chunks in
+        # one CTA per head, the twin; =0: token by token, the form of decode steps)
+        mode = os.environ.get("GOGGUF_B200_RETENTION_CHUNKED", "2")
+        self._many = mode == "2" and max(self.d, self.dv) <= K.RETENTION_CHUNKS_MAX_HEAD
+        self._chunked = mode != "0" and K.retention_chunk_takes(self.d, self.dv)
 
     def scale_output(self, mult: float) -> bool:
         """A factor on this mixer's output: it multiplies the gated heads in float32, before the output product."""
@@ -103,6 +106,13 @@ class RetentionMixer:
         cos, sin = self.position.tables(ctx)
         y = ctx.ws.get("retention_out", (T, H * dv), dt)
         raw = ctx.ws.get("retention_raw", (T, H * dv), torch.float32)
+        if self._many and ctx.max_new >= CHUNKED_FROM:
+            n = K.retention_chunks_scratch(T, ctx.n_seqs, H, d, dv)
+            K.retention_chunks(x, y, ctx.ws.get("retention_chunk_states", (n,), torch.float32), cache.state, cos, sin,
+                               ctx.cu_seqlens, ctx.slots, ctx.seq_of_token, self.decay, T, ctx.n_seqs, H, d, dv,
+                               self.rot, self.key_scale, self.eps, self.out_scale)
+            self.o(y, residual, accumulate=True, ws=ctx.ws)
+            return
         form = 1 if (self._chunked and ctx.max_new >= CHUNKED_FROM) else 0
         K.retention(x, y, raw, cache.state, cos, sin, ctx.cu_seqlens, ctx.slots, ctx.seq_of_token, self.decay,
                     T, ctx.n_seqs, H, d, dv, self.rot, self.key_scale, self.eps, self.out_scale, form)

@@ -220,7 +220,32 @@ def test_retention_mechanism_alone(dt, H, d, dv, rdims, decay):
                     T, len(sl), H, d, dv, rdims, d ** -0.5, eps, 1.7, form)
         return out.float().cpu()
 
+    def step_many(parts):
+        """The many-CTA chunked form on the same rows (no padding row: the step's own kernel zeroes those)."""
+        reqs = [(b, a, c) for b, (a, c) in enumerate(parts) if c]
+        x = torch.cat([rows[b][a:a + c] for b, a, c in reqs]).to(DEV).contiguous()
+        pos_t = torch.cat([torch.arange(a, a + c) for b, a, c in reqs]).to(torch.int32).to(DEV)
+        sot_t = torch.cat([torch.full((c,), i) for i, (b, a, c) in enumerate(reqs)]).to(torch.int32).to(DEV)
+        sl = torch.tensor([slots_of[b] for b, a, c in reqs], dtype=torch.int32, device=DEV)
+        cu = torch.tensor([0] + list(torch.tensor([c for b, a, c in reqs]).cumsum(0)), dtype=torch.int32, device=DEV)
+        T = x.shape[0]
+        cos, sin = _tables(r, pos_t)
+        out = torch.empty(T, H * dv, dtype=dt, device=DEV)
+        scratch = torch.empty(K.retention_chunks_scratch(T, len(reqs), H, d, dv), device=DEV)
+        K.retention_chunks(x, out, scratch, state, cos, sin, cu, sl, sot_t, dec, T, len(reqs), H, d, dv, rdims,
+                           d ** -0.5, eps, 1.7)
+        return out.float().cpu()
+
     limit = 3e-5 if dt == torch.float32 else 2e-2
+    if max(d, dv) <= K.RETENTION_CHUNKS_MAX_HEAD:
+        for s in slots_of:
+            state[s].zero_()
+        got = step_many([(0, 97), (0, 33), (0, 1)])
+        assert rel_err(got[:97], want[0][:97]) < limit and rel_err(got[97:130], want[1]) < limit
+        assert rel_err(got[130:131], want[2]) < limit
+        got = step_many([(97, 53), (0, 0), (0, 0)])                  # goes on from the state, to the prompt's end
+        assert rel_err(got, want[0][97:150]) < limit
+        assert float(state[5].min()) == 9.0
     for form in (0, 1) if chunk_ok else (0,):
         for s in slots_of:
             state[s].zero_()                                          # what opening a slot does
