@@ -407,6 +407,7 @@ __global__ void __launch_bounds__(256) ret_chunk_state_kernel(
     for (int i = 0; i < RET_PMAX / 16; ++i)
 #pragma unroll
         for (int j = 0; j < RET_PMAX / 16; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
         float kr[RET_PMAX / 16], vc[RET_PMAX / 16];
 #pragma unroll
@@ -447,14 +448,23 @@ __global__ void __launch_bounds__(256) ret_chunk_scan_kernel(
     for (int i = 0; i < RET_PC; ++i) aC *= a;
     float* sp = state + (((size_t)slots[b] * H + h) * d) * dv + e;
     float s = *sp;
-    for (int c = 0; c < nch; ++c) {
-        float* up = U + ((size_t)(base + c) * H + h) * d * dv + e;
-        const float u = *up;
-        *up = s;                           // the state the chunk starts from
-        const int n = min(RET_PC, n_new - c * RET_PC);
-        float an = aC;
-        if (n < RET_PC) { an = 1.f; for (int i = 0; i < n; ++i) an *= a; }
-        s = fmaf(s, an, u);
+    const size_t step = (size_t)H * d * dv;
+    float* up = U + ((size_t)base * H + h) * d * dv + e;
+    // eight chunks' additions are asked for at once: the walk itself is a chain of dependent multiply-adds only
+    for (int c0 = 0; c0 < nch; c0 += 8) {
+        float u[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) u[k] = c0 + k < nch ? up[(size_t)(c0 + k) * step] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < nch) {
+                up[(size_t)(c0 + k) * step] = s;           // the state the chunk starts from
+                const int n = min(RET_PC, n_new - (c0 + k) * RET_PC);
+                float an = aC;
+                if (n < RET_PC) { an = 1.f; for (int i = 0; i < n; ++i) an *= a; }
+                s = fmaf(s, an, u[k]);
+            }
+        }
     }
     *sp = s;
 }
@@ -490,6 +500,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
         for (int i = 0; i < RET_PC / 16; ++i)
 #pragma unroll
             for (int j = 0; j < RET_PC / 16; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
         for (int r = 0; r < d; ++r) {
             float qv[RET_PC / 16], kv[RET_PC / 16];
 #pragma unroll
@@ -517,6 +528,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
 #pragma unroll
         for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] = 0.f;
     const float* S = Sin + ((size_t)blockIdx.x * H + h) * d * dv;
+#pragma unroll 4
     for (int r = 0; r < d; ++r) {
         float qv[RET_PC / 16], sv[RET_PMAX / 16];
 #pragma unroll
@@ -535,6 +547,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
         for (int c = 0; c < RET_PMAX / 16; ++c) o[i][c] *= f;
     }
     __syncthreads();                          // A is whole; every thread is done with the q rows
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
         float av[RET_PC / 16], vv[RET_PMAX / 16];
 #pragma unroll
