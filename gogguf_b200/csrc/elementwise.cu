@@ -493,24 +493,54 @@ GG_API gg_qkv_prep(const void* qkv, int dtype, void* q_out, const float* qw, con
 // ----------------------------------------------------------------------------- norm of a part's output, added
 // x[r, :] += y[r, :] / sqrt(mean(y[r, :]^2) + eps) * w: the norm that follows a part in a block with norms on
 // both sides of its parts, and the add into the residual stream, in one pass.  All float32; one block per row.
+// With xhat and ssq it also leaves what a product with a folded norm reads of the updated row: its bfloat16 copy
+// and the sums of its squares over blocks of 128 columns (see row_stats_kernel), so the norm before the next
+// part needs no kernel of its own.
 __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float* y, const float* __restrict__ w,
-                                                          int H, float eps) {
+                                                          int H, float eps, bf16* __restrict__ xhat,
+                                                          float* __restrict__ ssq, int parts) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
+    extern __shared__ float psum[];          // [parts][4]: a 128-column block is four warps' 32 columns
     const size_t r = blockIdx.x;
     const float* yr = y + r * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     const float f = 1.0f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) x[r * H + i] += yr[i] * f * w[i];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i0 = 0; i0 < H; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        float v = 0.f;
+        if (i < H) {
+            v = x[r * H + i] + yr[i] * f * w[i];
+            x[r * H + i] = v;
+            if (xhat != nullptr) xhat[r * H + i] = __float2bfloat16_rn(v);
+        }
+        if (ssq != nullptr) {
+            const float q = warp_sum(v * v);
+            const int part = (i0 >> 7) + (warp >> 2);
+            if (lane == 0 && part < parts) psum[part * 4 + (warp & 3)] = q;
+        }
+    }
+    if (ssq != nullptr) {
+        __syncthreads();
+        for (int p = threadIdx.x; p < parts; p += blockDim.x)
+            ssq[r * parts + p] = (psum[p * 4] + psum[p * 4 + 1]) + (psum[p * 4 + 2] + psum[p * 4 + 3]);
+    }
 }
 
-GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H, float eps, cudaStream_t stream) {
+// xhat (bfloat16 [rows, H]) and ssq (float32 [rows, ceil(H / 128)]) may both be null.
+GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H, float eps, void* xhat, float* ssq,
+                      cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (H <= 0) return GG_ERR_ARG;
-    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), 0, stream, 1, x, y, w, H, eps);
+    if (H <= 0 || (xhat == nullptr) != (ssq == nullptr)) return GG_ERR_ARG;
+    const int parts = (H + 127) / 128;
+    // (a block of 128 columns whose tail lies beyond H gets zeros from the warps that have no column)
+    const size_t smem = ssq != nullptr ? ((size_t)(parts + 1) * 4) * sizeof(float) : 0;
+    if (smem > 48 * 1024) return GG_ERR_ARG;
+    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), smem, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts);
     return gg_last_error();
 }
 

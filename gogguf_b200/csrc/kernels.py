@@ -131,15 +131,26 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
         n_tokens, nq, nkv, d, dv, rot, _p(status_word(qkv.device)), _stream())
 
 
-def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-    """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32."""
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None) -> None:
+    """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32.  With `xhat` (bfloat16 like x) and `ssq`
+    (float32 [rows, ceil(H / 128)]) the updated rows' bfloat16 copy and sums of squares per 128 columns are left too
+    (what `row_stats` makes)."""
     _need(x, torch.float32, "x")
     _need(y, torch.float32, "y")
     _need(weight, torch.float32, "norm weight")
     H = x.shape[-1]
     if y.shape != x.shape or weight.numel() != H:
         raise KernelError("rmsnorm_add: shapes disagree")
-    kernel("elementwise", "gg_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, float(eps), _stream())
+    if (xhat is None) != (ssq is None):
+        raise KernelError("rmsnorm_add: xhat and ssq come together")
+    if xhat is not None:
+        _need(xhat, torch.bfloat16, "xhat")
+        _need(ssq, torch.float32, "ssq")
+        if xhat.numel() != x.numel() or ssq.numel() != (x.numel() // H) * ((H + 127) // 128):
+            raise KernelError("rmsnorm_add: shapes of xhat / ssq disagree")
+    kernel("elementwise", "gg_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, float(eps), _p(xhat), _p(ssq),
+                                             _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:

@@ -125,9 +125,12 @@ class AttentionMixer:
         self._fused_rope = (self.qkv.tensor_core and self.d == 128 and self.rot == self.d and not self._general
                             and os.environ.get("GOGGUF_B200_FUSE_QKV_ROPE", "1") != "0")
 
+    def can_absorb_norm(self, norm) -> bool:
+        return self.qkv.can_fold and norm.size == self.hidden
+
     def absorb_norm(self, norm) -> bool:
         """Take the block's pre-norm into the q/k/v projection; `forward` then gets RowStats as `h`."""
-        if not self.qkv.can_fold or norm.size != self.hidden:
+        if not self.can_absorb_norm(norm):
             return False
         self.qkv.fold_input_norm(norm.weight, norm.eps)
         return True

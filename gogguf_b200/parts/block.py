@@ -107,6 +107,8 @@ class SandwichNormBlock:
     roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
              "feed_forward_norm": "norm", "feed_forward_post_norm": "norm"}
     optional_roles = ("feed_forward", "feed_forward_norm", "feed_forward_post_norm")
+    keeps_row_stats = True      # its statistics are its own (see `forward`); it clears and sets `fresh` itself
+    STATS = "sandwich_row_stats"
 
     def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
         self.parts = dict(parts)
@@ -119,20 +121,46 @@ class SandwichNormBlock:
         for post in (self.mixer_post, self.ff_post):
             if post is not None and not getattr(post, "foldable", False):
                 raise ValueError("sandwich_norm: the norm after a part must be y / rms(y) * weight")
+        # A part may take the norm before it into its first projection (`absorb_norm(norm) -> bool`); it then reads
+        # the residual's RowStats, which the norm-and-add kernel of the part before it has left behind.
+        self.mixer_folded = _offer_norm(self.mixer, self.mixer_norm, rt)
+        self.ff_folded = self.feed_forward is not None and _offer_norm(self.feed_forward, self.ff_norm, rt)
+        self.any_folded = self.mixer_folded or self.ff_folded
 
-    def _part(self, x: torch.Tensor, ctx: StepContext, pre, post, call) -> None:
-        h = ctx.ws.get("block_normed", tuple(x.shape), self.rt.dtype)
-        pre.forward(x, h)
+    def _part(self, x: torch.Tensor, ctx: StepContext, pre, post, call, folded: bool, stats, emit: bool) -> None:
+        if folded:
+            h = stats.ensure(x)
+        else:
+            h = ctx.ws.get("block_normed", tuple(x.shape), self.rt.dtype)
+            pre.forward(x, h)
         y = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
         y.zero_()
         call(h, y)
-        K.rmsnorm_add(x, y, post.weight, post.eps)
+        if stats is not None and emit:
+            K.rmsnorm_add(x, y, post.weight, post.eps, xhat=stats.xhat, ssq=stats.ssq)
+            stats.fresh = True
+        else:
+            K.rmsnorm_add(x, y, post.weight, post.eps)
+            if stats is not None:
+                stats.fresh = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache, writes_cache: bool) -> None:
+        # The statistics live under a key of this arrangement's own: a part's last product writes into the part's
+        # output buffer here, not into the residual stream, and must not be offered the stream's statistics.
+        stats = ctx.shared.get(self.STATS)
+        if stats is None and self.any_folded:
+            T, H = x.shape
+            stats = ctx.shared[self.STATS] = RowStats(
+                ctx.ws.get("residual_bf16", (T, H), torch.bfloat16),
+                ctx.ws.get("residual_ssq", (T, (H + 127) // 128), torch.float32))
+        # the norm-and-add after a part leaves the statistics where the part that comes next in this block reads them
+        # folded; across blocks it always does (the next block may be of another make: it re-makes what is stale)
         self._part(x, ctx, self.mixer_norm, self.mixer_post,
-                   lambda h, y: self.mixer.forward(h, y, ctx, cache, writes_cache))
+                   lambda h, y: self.mixer.forward(h, y, ctx, cache, writes_cache), self.mixer_folded, stats,
+                   emit=self.feed_forward is None or self.ff_folded)
         if self.feed_forward is not None:
-            self._part(x, ctx, self.ff_norm, self.ff_post, lambda h, y: self.feed_forward.forward(h, y, ctx))
+            self._part(x, ctx, self.ff_norm, self.ff_post, lambda h, y: self.feed_forward.forward(h, y, ctx),
+                       self.ff_folded, stats, emit=True)
 
 
 def _offer_norm(part, norm, rt: Runtime) -> bool:

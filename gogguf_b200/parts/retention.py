@@ -86,6 +86,16 @@ class RetentionMixer:
         self._many = mode == "2" and max(self.d, self.dv) <= K.RETENTION_CHUNKS_MAX_HEAD
         self._chunked = mode != "0" and K.retention_chunk_takes(self.d, self.dv)
 
+    def can_absorb_norm(self, norm) -> bool:
+        return self.qkvg.can_fold and norm.size == self.hidden
+
+    def absorb_norm(self, norm) -> bool:
+        """Take the block's pre-norm into the q/k/v/gate projection; `forward` then gets RowStats as `h`."""
+        if not self.can_absorb_norm(norm):
+            return False
+        self.qkvg.fold_input_norm(norm.weight, norm.eps)
+        return True
+
     def scale_output(self, mult: float) -> bool:
         """A factor on this mixer's output: it multiplies the gated heads in float32, before the output product."""
         self.out_scale = float(mult)

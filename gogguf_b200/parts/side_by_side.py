@@ -56,6 +56,14 @@ class SideBySideMixer:
             direct = w == 1.0 or (take is not None and bool(take(w)))
             self.members.append((part, w, direct))
 
+    def absorb_norm(self, norm) -> bool:
+        """The norm before this mixer goes into every member's first projection, or into none: all members read
+        the same input."""
+        parts = [p for p, _, _ in self.members]
+        if not all(getattr(p, "can_absorb_norm", None) is not None and p.can_absorb_norm(norm) for p in parts):
+            return False
+        return all([bool(p.absorb_norm(norm)) for p in parts])
+
     @property
     def capturable(self) -> bool:
         return all(getattr(p, "capturable", True) for p, _, _ in self.members)
