@@ -531,12 +531,63 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float*
     }
 }
 
+// The same with 16-byte accesses (H a multiple of 4, rows on 16-byte boundaries): a thread owns four columns, a
+// warp the 128 columns of one block of the sums of squares, so those need no shared memory.
+__global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, const float* y, const float* __restrict__ w,
+                                                               int H, float eps, bf16* __restrict__ xhat,
+                                                               float* __restrict__ ssq, int parts) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const float4* yr = reinterpret_cast<const float4*>(y + r * H);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4* xr = reinterpret_cast<float4*>(x + r * H);
+    const int n4 = H >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        const float4 v = yr[i];
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float f = 1.0f / sqrtf(ss / (float)H + eps);
+    const int lane = threadIdx.x & 31;
+    for (int i0 = 0; i0 < n4; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        float q = 0.f;
+        if (i < n4) {
+            const float4 a = xr[i], b = yr[i], c = wr[i];
+            float4 v;
+            v.x = a.x + b.x * f * c.x; v.y = a.y + b.y * f * c.y; v.z = a.z + b.z * f * c.z; v.w = a.w + b.w * f * c.w;
+            xr[i] = v;
+            if (xhat != nullptr) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                *reinterpret_cast<uint2*>(xhat + r * H + 4 * (size_t)i) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+            q = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+        if (ssq != nullptr) {
+            q = warp_sum(q);
+            const int part = (i - lane) >> 5;             // the warp's first column / 128
+            if (lane == 0 && part < parts) ssq[r * parts + part] = q;
+        }
+    }
+}
+
 // xhat (bfloat16 [rows, H]) and ssq (float32 [rows, ceil(H / 128)]) may both be null.
 GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H, float eps, void* xhat, float* ssq,
                       cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0 || (xhat == nullptr) != (ssq == nullptr)) return GG_ERR_ARG;
     const int parts = (H + 127) / 128;
+    if ((H & 3) == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w) & 15) == 0 && (((uintptr_t)xhat) & 7) == 0) {
+        // few rows (decode steps): as many threads as the row has groups of four columns, up to 1,024
+        int threads = ((H >> 2) + 31) / 32 * 32;
+        if (threads > 1024 || rows >= 512) threads = threads > 256 ? 256 : threads;
+        gg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts);
+        return gg_last_error();
+    }
     // (a block of 128 columns whose tail lies beyond H gets zeros from the warps that have no column)
     const size_t smem = ssq != nullptr ? ((size_t)(parts + 1) * 4) * sizeof(float) : 0;
     if (smem > 48 * 1024) return GG_ERR_ARG;

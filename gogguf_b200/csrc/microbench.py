@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent] [--m 1,8,64] [--ctx 2048,8192]
+"""Kernel micro-benchmarks: python -m gogguf_b200.csrc.microbench [gemm|gemm_layer|attn|prefill_attn|sample|latent|retention] [--m 1,8,64] [--ctx 2048,8192]
 
 Times single kernels the way a decode step runs them: forty launches captured in a CUDA graph and
 replayed, so that host launch cost is out of the picture and dependent launches overlap as they do
@@ -263,9 +263,71 @@ def latent(sizes=((16, 64, 32, 64, 256, 1024, 2048), (32, 128, 64, 128, 512, 204
         torch.cuda.empty_cache()
 
 
+def retention(sizes=((8, 128, 128, 2048), (16, 128, 128, 4096))) -> None:
+    """Retention (csrc/retention.cu) at layer sizes (heads, d, dv, width): a prompt of 2,048 tokens over many CTAs
+    against the float32 multiply-add rate of the CUDA cores (the design asks for 32-bit there, so the tensor cores
+    are not its roofline), decode steps against the copy bandwidth (a step reads and writes every state), and the
+    norm-and-add kernel of the sandwich-norm blocks."""
+    from . import kernels as K
+    dev = "cuda:0"
+    hbm, _, src = _peaks()
+    props = torch.cuda.get_device_properties(0)
+    fp32_tflops = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12      # FMA lanes x 2 x the highest SM clock
+    print(f"peaks ({src}): {hbm:.0f} GB/s copy; float32 multiply-add rate {fp32_tflops:.1f} TFLOP/s (nominal, 1,965 MHz)")
+    for H, d, dv, W in sizes:
+        width = 2 * H * (d + dv)
+        decay = torch.linspace(0.97, 0.9995, H, device=dev)
+        T = 2048
+        nbuf = 4
+        xs = [(torch.randn(T, width, device=dev) * 0.5).to(torch.bfloat16) for _ in range(nbuf)]
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        inv = torch.pow(torch.tensor(1e6, dtype=torch.float64), -torch.arange(16, dtype=torch.float64) / 16).to(dev)
+        cos, sin = torch.empty(T, 16, device=dev), torch.empty(T, 16, device=dev)
+        K.rope_tables(pos, inv, cos, sin)
+        out = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        state = torch.zeros(1, H, d, dv, device=dev)
+        scratch = torch.empty(K.retention_chunks_scratch(T, 1, H, d, dv), device=dev)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        sot = torch.zeros(T, dtype=torch.int32, device=dev)
+        us = _time_graph(lambda i: K.retention_chunks(xs[i % nbuf], out, scratch, state, cos, sin, cu, zero, sot, decay,
+                                                      T, 1, H, d, dv, 32, d ** -0.5, 1e-6, 1.0), reps=10)
+        C = K.RETENTION_CHUNK
+        flops = 2 * T * H * (2 * d * dv + C * (d + dv) / 2)
+        print(f"retention prompt  H={H} d={d} dv={dv} T={T}: {us:8.1f} us  {flops / us / 1e6:6.2f} TFLOP/s "
+              f"({flops / us / 1e6 / fp32_tflops:.2f} of the float32 rate)", flush=True)
+        for B in (8, 64):
+            slots = 512 // B * B
+            st = torch.zeros(slots, H, d, dv, device=dev)       # 512 states: 32 to 64 MB a head count, beyond L2 in turns
+            x1 = (torch.randn(B, width, device=dev) * 0.5).to(torch.bfloat16)
+            o1 = torch.empty(B, H * dv, device=dev, dtype=torch.bfloat16)
+            raw = torch.empty(B, H * dv, device=dev)
+            cu1 = torch.arange(B + 1, dtype=torch.int32, device=dev)
+            sot1 = torch.arange(B, dtype=torch.int32, device=dev)
+            sl = [torch.arange(k * B, (k + 1) * B, dtype=torch.int32, device=dev) for k in range(slots // B)]
+            us = _time_graph(lambda i: K.retention(x1, o1, raw, st, cos, sin, cu1, sl[i % len(sl)], sot1, decay, B, B, H, d,
+                                                   dv, 32, d ** -0.5, 1e-6, 1.0, 0))
+            nbytes = 2 * B * H * d * dv * 4
+            print(f"retention decode  H={H} d={d} dv={dv} batch {B:3d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        for rows in (8, 64, 2048):
+            n = max(2, int(300e6 // (rows * W * 12)) + 1) if rows >= 2048 else 2
+            x = [torch.randn(rows, W, device=dev) for _ in range(n)]
+            y = [torch.randn(rows, W, device=dev) for _ in range(n)]
+            w = torch.ones(W, device=dev)
+            xh = torch.empty(rows, W, device=dev, dtype=torch.bfloat16)
+            sq = torch.empty(rows, (W + 127) // 128, device=dev)
+            us = _time_graph(lambda i: K.rmsnorm_add(x[i % n], y[i % n], w, 1e-6, xhat=xh, ssq=sq))
+            nbytes = rows * W * (4 + 4 + 4 + 2)
+            print(f"norm-and-add      width {W} rows {rows:4d}: {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s "
+                  f"({nbytes / us / 1e3 / hbm:.2f} of the copy bandwidth)", flush=True)
+        del xs
+        torch.cuda.empty_cache()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent"])
+    ap.add_argument("what", choices=["gemm", "gemm_layer", "attn", "prefill_attn", "sample", "latent", "retention"])
     ap.add_argument("--m", default="1,8,64", help="token counts (gemm), batch sizes (attn) or prompt lengths (prefill_attn)")
     ap.add_argument("--ctx", default="2048", help="attn: cached positions per sequence (comma separated)")
     ap.add_argument("--scratch", action="store_true", help="attn: splits merged by a second kernel instead of inside clusters")
@@ -273,6 +335,9 @@ def main() -> None:
     ms = [int(x) for x in a.m.split(",")]
     if a.what == "latent":
         latent()
+        return
+    if a.what == "retention":
+        retention()
         return
     if a.what == "attn":
         for c in a.ctx.split(","):

@@ -315,12 +315,21 @@ def test_tensor_core_attention_with_a_sink_and_a_factor(d, nq, nkv, window):
 def test_norm_of_a_parts_output_added_to_the_stream():
     K = _K()
     g = torch.Generator().manual_seed(2)
-    for rows, H in ((5, 96), (3, 1000), (1, 7)):
+    for rows, H in ((5, 96), (3, 1000), (1, 7), (2, 4096), (600, 2048), (4, 200), (2, 8200)):
         x, y, w = torch.randn(rows, H, generator=g), torch.randn(rows, H, generator=g) * 3, torch.randn(H, generator=g)
         want = x.double() + plain.wnorm(y.double(), w.double(), 1e-5)
         xd = x.to(DEV)
         K.rmsnorm_add(xd, y.to(DEV), w.to(DEV), 1e-5)
         assert rel_err(xd, want) < 2e-6
+        # the same with what a product with a folded norm reads of the updated rows
+        xd2 = x.to(DEV)
+        parts = (H + 127) // 128
+        xhat = torch.zeros(rows, H, dtype=torch.bfloat16, device=DEV)
+        ssq = torch.full((rows, parts), -1.0, device=DEV)
+        K.rmsnorm_add(xd2, y.to(DEV), w.to(DEV), 1e-5, xhat=xhat, ssq=ssq)
+        assert torch.equal(xd2, xd) and torch.equal(xhat, xd.to(torch.bfloat16))
+        sq = torch.nn.functional.pad(want ** 2, (0, parts * 128 - H)).view(rows, parts, 128).sum(-1)
+        assert rel_err(ssq, sq) < 2e-6
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
