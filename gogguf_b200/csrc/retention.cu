@@ -346,7 +346,10 @@ __device__ __forceinline__ bool ret_find_chunk(int item, const int* cu_seqlens, 
 template <typename T>
 __device__ __forceinline__ void ret_stage(const T* qkvg, int ld, int t0, int n, int h, int H, int d, int dv, int rot,
                                           float kscale, const float* cosv, const float* sinv, float* qs, float* ks,
-                                          float* vs, int ds, const float* wk) {
+                                          float* vs, int ds, const float* wk, int qstride = 0, bool swizzle = false) {
+    // swizzle: element i of row tt goes to column i ^ (tt & 31) of an unpadded row (d a multiple of 32): rows that
+    // differ in their low five bits then read one column from different banks, as a padded row would give them
+    if (qstride == 0) qstride = ds;
     const int half = rot >> 1;
     for (int idx = threadIdx.x; idx < n * d; idx += blockDim.x) {
         const int tt = idx / d, i = idx - tt * d;
@@ -369,8 +372,8 @@ __device__ __forceinline__ void ret_stage(const T* qkvg, int ld, int t0, int n, 
             if (qs) qv = to_f<T>(qp[i]);
             kv = to_f<T>(kp[i]);
         }
-        if (qs) qs[tt * ds + i] = qv;
-        ks[tt * ds + i] = kv * kscale * (wk ? wk[tt] : 1.f);
+        if (qs) qs[tt * qstride + i] = qv;
+        ks[tt * ds + (swizzle ? (i ^ (tt & 31)) : i)] = kv * kscale * (wk ? wk[tt] : 1.f);
     }
     for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
         const int tt = idx / dv, j = idx - tt * dv;
@@ -470,7 +473,7 @@ __global__ void __launch_bounds__(256) ret_chunk_scan_kernel(
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) ret_chunk_out_kernel(
+__global__ void __launch_bounds__(256, 2) ret_chunk_out_kernel(
     const T* qkvg, int ld, T* out, const float* Sin, const float* cosv, const float* sinv,
     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token, const float* __restrict__ decay,
     int n_seqs, int H, int d, int dv, int rot, float kscale, float eps, float out_scale) {
@@ -479,19 +482,22 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
     extern __shared__ float sm[];
     int b, t0, n;
     if (!ret_find_chunk(blockIdx.x, cu_seqlens, seq_of_token, n_seqs, b, t0, n)) return;
-    const int h = blockIdx.y, ds = d + 1, wide = max(ds, dv);
-    float* qs = sm;                           // [PC][wide]: q rows (stride ds), later the raw outputs (stride dv)
+    // Shared memory is cut so that two CTAs share an SM at 128 x 128 heads: q rows unpadded (read as broadcasts),
+    // k rows unpadded with swizzled columns where d is a multiple of 32 (else padded by one), A without padding.
+    const bool swz = (d & 31) == 0;
+    const int h = blockIdx.y, ds = swz ? d : d + 1, wide = max(d, dv);
+    float* qs = sm;                           // [PC][wide]: q rows (stride d), later the raw outputs (stride dv)
     float* ks = qs + RET_PC * wide;           // [PC][ds]
     float* vs = ks + RET_PC * ds;             // [PC][dv]
-    float* A = vs + RET_PC * dv;              // [PC][PC + 1]
-    float* pw = A + RET_PC * (RET_PC + 1);    // [PC + 1]
+    float* A = vs + RET_PC * dv;              // [PC][PC]
+    float* pw = A + RET_PC * RET_PC;          // [PC + 1]
     const float a = decay[h];
     if (threadIdx.x <= RET_PC) {
         float p = 1.f;
         for (int i = 0; i < (int)threadIdx.x; ++i) p *= a;
         pw[threadIdx.x] = p;
     }
-    ret_stage<T>(qkvg, ld, t0, n, h, H, d, dv, rot, kscale, cosv, sinv, qs, ks, vs, ds, nullptr);
+    ret_stage<T>(qkvg, ld, t0, n, h, H, d, dv, rot, kscale, cosv, sinv, qs, ks, vs, ds, nullptr, d, swz);
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     {   // A[i][j] = decay^(i-j) (q_i . k_j) for j <= i < n, else 0
@@ -505,8 +511,8 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
             float qv[RET_PC / 16], kv[RET_PC / 16];
 #pragma unroll
             for (int i = 0; i < RET_PC / 16; ++i) {
-                qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * ds + r] : 0.f;
-                kv[i] = tx + 16 * i < n ? ks[(tx + 16 * i) * ds + r] : 0.f;
+                qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * d + r] : 0.f;
+                kv[i] = tx + 16 * i < n ? ks[(tx + 16 * i) * ds + (swz ? (r ^ ((tx + 16 * i) & 31)) : r)] : 0.f;
             }
 #pragma unroll
             for (int i = 0; i < RET_PC / 16; ++i)
@@ -518,7 +524,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
 #pragma unroll
             for (int j = 0; j < RET_PC / 16; ++j) {
                 const int qi = ty + 16 * i, kj = tx + 16 * j;
-                A[qi * (RET_PC + 1) + kj] = (kj <= qi && qi < n) ? acc[i][j] * pw[qi - kj] : 0.f;
+                A[qi * RET_PC + kj] = (kj <= qi && qi < n) ? acc[i][j] * pw[qi - kj] : 0.f;
             }
     }
     // o[i][c]: rows i = ty + 16 a, columns c = tx + 16 b
@@ -532,7 +538,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
     for (int r = 0; r < d; ++r) {
         float qv[RET_PC / 16], sv[RET_PMAX / 16];
 #pragma unroll
-        for (int i = 0; i < RET_PC / 16; ++i) qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * ds + r] : 0.f;
+        for (int i = 0; i < RET_PC / 16; ++i) qv[i] = ty + 16 * i < n ? qs[(ty + 16 * i) * d + r] : 0.f;
 #pragma unroll
         for (int c = 0; c < RET_PMAX / 16; ++c) sv[c] = tx + 16 * c < dv ? S[(size_t)r * dv + tx + 16 * c] : 0.f;
 #pragma unroll
@@ -551,7 +557,7 @@ __global__ void __launch_bounds__(256) ret_chunk_out_kernel(
     for (int j = 0; j < n; ++j) {
         float av[RET_PC / 16], vv[RET_PMAX / 16];
 #pragma unroll
-        for (int i = 0; i < RET_PC / 16; ++i) av[i] = A[(ty + 16 * i) * (RET_PC + 1) + j];
+        for (int i = 0; i < RET_PC / 16; ++i) av[i] = A[(ty + 16 * i) * RET_PC + j];
 #pragma unroll
         for (int c = 0; c < RET_PMAX / 16; ++c) vv[c] = tx + 16 * c < dv ? vs[j * dv + tx + 16 * c] : 0.f;
 #pragma unroll
@@ -597,9 +603,9 @@ GG_API gg_retention_chunks(const void* qkvg, int dtype, int ld, void* out, float
     if (ntok <= 0 || n_seqs <= 0) return 0;
     if (H <= 0 || H > 65535 || d <= 0 || dv <= 0 || d > RET_PMAX || dv > RET_PMAX || rot < 0 || rot > d || (rot & 1) ||
         scratch == nullptr) return GG_ERR_ARG;
-    const int chunks = ntok / RET_PC + n_seqs, ds = d + 1, wide = ds > dv ? ds : dv;
+    const int chunks = ntok / RET_PC + n_seqs, ds = d + 1, wide = d > dv ? d : dv;
     const size_t smem_a = ((size_t)RET_PC * (ds + dv + 1)) * sizeof(float);
-    const size_t smem_c = ((size_t)RET_PC * (wide + ds + dv + RET_PC + 1) + RET_PC + 1) * sizeof(float);
+    const size_t smem_c = ((size_t)RET_PC * (wide + ((d & 31) == 0 ? d : d + 1) + dv + RET_PC) + RET_PC + 1) * sizeof(float);
     GG_DISPATCH_DTYPE(dtype, T,
         if (smem_a > 48 * 1024)
             cudaFuncSetAttribute(ret_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
