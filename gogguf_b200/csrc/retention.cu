@@ -25,8 +25,10 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 template <typename T>
 __device__ __forceinline__ void ret_load_rows(const T* qkvg, int ld, int t0, int nb, int h, int H, int d, int dv,
                                               int rot, float kscale, const float* cosv, const float* sinv,
-                                              float* qs, float* ks, float* vs, int j0, int ncols, int vstride) {
+                                              float* qs, float* ks, float* vs, int j0, int ncols, int vstride,
+                                              int qstride = 0) {
     const int half = rot >> 1;
+    if (qstride == 0) qstride = d;
     for (int idx = threadIdx.x; idx < nb * d; idx += blockDim.x) {
         const int tt = idx / d, i = idx - tt * d;
         const T* row = qkvg + (size_t)(t0 + tt) * ld;
@@ -48,8 +50,8 @@ __device__ __forceinline__ void ret_load_rows(const T* qkvg, int ld, int t0, int
             qv = to_f<T>(qp[i]);
             kv = to_f<T>(kp[i]);
         }
-        qs[tt * d + i] = qv;
-        ks[tt * d + i] = kv * kscale;
+        qs[tt * qstride + i] = qv;
+        ks[tt * qstride + i] = kv * kscale;
     }
     for (int idx = threadIdx.x; idx < nb * ncols; idx += blockDim.x) {
         const int tt = idx / ncols, j = idx - tt * ncols;
@@ -61,7 +63,7 @@ __device__ __forceinline__ void ret_load_rows(const T* qkvg, int ld, int t0, int
 // the rows part*RPT .. part*RPT+RPT-1 of column j0 + j of the state.  fused != 0 (one column tile): the block
 // norms, gates and stores the outputs itself; else it leaves the raw float32 outputs in `raw` [T, H*dv].
 template <typename T, int RPT>
-__global__ void __launch_bounds__(RET_MAX_THREADS) retention_scan_kernel(
+__global__ void __launch_bounds__(RET_MAX_THREADS, 1) retention_scan_kernel(
     const T* qkvg, int ld, T* out, float* raw, float* state,
     const float* cosv, const float* sinv, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
     const int* __restrict__ seq_of_token, const float* __restrict__ decay,
@@ -71,9 +73,10 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_scan_kernel(
     extern __shared__ float sm[];
     const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
     const int ncols = min(cols, dv - j0);
-    float* qs = sm;                            // [RET_TB][d]
-    float* ks = qs + RET_TB * d;               // [RET_TB][d]
-    float* vs = ks + RET_TB * d;               // [RET_TB][cols]
+    const int dp = parts * RPT;                // d rounded up to the threads' shares; the tail holds zeros
+    float* qs = sm;                            // [RET_TB][dp]
+    float* ks = qs + RET_TB * dp;              // [RET_TB][dp]
+    float* vs = ks + RET_TB * dp;              // [RET_TB][cols]
     float* os = vs + RET_TB * cols;            // [RET_TB][parts][cols]
     const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
     if (end <= start) return;
@@ -94,24 +97,32 @@ __global__ void __launch_bounds__(RET_MAX_THREADS) retention_scan_kernel(
 #pragma unroll
     for (int i = 0; i < RPT; ++i) S[i] = (live && r0 + i < d) ? sp[(size_t)(r0 + i) * dv] : 0.f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    if (dp > d)
+        for (int idx = threadIdx.x; idx < RET_TB * (dp - d); idx += blockDim.x) {
+            const int tt = idx / (dp - d), i = d + idx % (dp - d);
+            qs[tt * dp + i] = 0.f;
+            ks[tt * dp + i] = 0.f;
+        }
     for (int t0 = start; t0 < end; t0 += RET_TB) {
         const int nb = min(RET_TB, end - t0);
-        ret_load_rows<T>(qkvg, ld, t0, nb, h, H, d, dv, rot, kscale, cosv, sinv, qs, ks, vs, j0, ncols, cols);
+        ret_load_rows<T>(qkvg, ld, t0, nb, h, H, d, dv, rot, kscale, cosv, sinv, qs, ks, vs, j0, ncols, cols, dp);
         __syncthreads();
         if (live) {
+#pragma unroll 1
             for (int tt = 0; tt < nb; ++tt) {
                 const float vj = vs[tt * cols + j];
-                const float* kt = ks + tt * d + r0;
-                const float* qt = qs + tt * d + r0;
-                float o = 0.f;
+                const float* kt = ks + tt * dp + r0;
+                const float* qt = qs + tt * dp + r0;
+                // (rows of the thread's share that lie beyond d hold zeros in k and q: no test in the loop)
+                float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    if (r0 + i < d) {
-                        S[i] = fmaf(a, S[i], kt[i] * vj);
-                        o = fmaf(S[i], qt[i], o);
-                    }
+                for (int i = 0; i < RPT; i += 2) {
+                    S[i] = fmaf(a, S[i], kt[i] * vj);
+                    S[i + 1] = fmaf(a, S[i + 1], kt[i + 1] * vj);
+                    o0 = fmaf(S[i], qt[i], o0);
+                    o1 = fmaf(S[i + 1], qt[i + 1], o1);
                 }
-                os[(tt * parts + part) * cols + j] = o;
+                os[(tt * parts + part) * cols + j] = o0 + o1;
             }
         }
         __syncthreads();
@@ -287,7 +298,9 @@ GG_API gg_retention(const void* qkvg, int dtype, int ld, void* out, float* raw, 
         return gg_last_error();
     }
     const int dvp = (dv + 31) / 32 * 32;
-    const int rpt = ((d + 31) / 32) * dvp <= 256 ? 32 : 64;
+    // 32 rows of the state per thread keep it in registers (64 spill at 512 threads a block); 64 only where the
+    // head's rows would otherwise need more parts than a block has warps
+    const int rpt = (d + 31) / 32 <= RET_MAX_THREADS / 32 ? 32 : 64;
     const int parts = (d + rpt - 1) / rpt;
     int cols = RET_MAX_THREADS / parts / 32 * 32;
     if (cols <= 0) return GG_ERR_ARG;
@@ -295,7 +308,7 @@ GG_API gg_retention(const void* qkvg, int dtype, int ld, void* out, float* raw, 
     const int tiles = (dv + cols - 1) / cols;
     const int fused = tiles == 1;
     if (!fused && raw == nullptr) return GG_ERR_ARG;
-    const size_t smem = ((size_t)2 * RET_TB * d + (size_t)RET_TB * cols * (1 + parts)) * sizeof(float);
+    const size_t smem = ((size_t)2 * RET_TB * parts * rpt + (size_t)RET_TB * cols * (1 + parts)) * sizeof(float);
     if (smem > 200 * 1024) return GG_ERR_ARG;
 #define GG_RET_SCAN(T_, R_)                                                                                          \
     do {                                                                                                             \
