@@ -194,13 +194,13 @@ def sokirax_config(z, kind):
     import math
     H, G, W = z["heads"], z["kv_heads"], z["width"]
     a = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=z["window"]),
-             rot=dict(base=1000000.0, dims=64, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+             rot=dict(base=500000.0, dims=64, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0)))
     left = dict(heads=H, kv_heads=G, dim=64, vdim=64, scale=0.125, mask=dict(size=z["window"]),
-                rot=dict(base=250000.0, dims=32))
+                rot=dict(base=100000.0, dims=32))
     R = z["ret_heads"]
-    right = dict(heads=R, dim=128, vdim=128, rot=dict(base=1000000.0, dims=32),
+    right = dict(heads=R, dim=128, vdim=128, rot=dict(base=500000.0, dims=32),
                  decay=[1.0 - 2.0 ** (-5.0 - 7.0 * i / max(R - 1, 1)) for i in range(R)])
-    p = dict(left=left, right=right, left_scale=1.2, right_scale=1.1)
+    p = dict(left=left, right=right, left_scale=1.0, right_scale=0.9)
     mlp = dict(kind="dense", ff=(2 * z["ff"] // 3) // 128 * 128) if kind == "dense" else dict(
         kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]),
         shared=dict(ff=z["shared_ff"]))

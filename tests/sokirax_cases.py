@@ -77,7 +77,7 @@ CASE_ONE = dict(
 CASE_W = dict(
     architecture="Sokirax", vocab=523, width=256, norm=dict(eps=3e-6),
     layers=[
-        layer("attention", attn(4, 1, 128, 128, 0.09, 150, rot(100000.0, 64, (8.0, 256, 32.0, 1.0))), moe(128, 6, 2, shared=192)),
+        layer("attention", attn(4, 1, 128, 128, 0.09, 150, rot(100000.0, 64, (6.0, 256, 24.0, 1.5))), moe(128, 6, 2, shared=192)),
         layer("parallel", par(attn(8, 2, 64, 64, 0.12, 90, rot(10000.0, 32)),
                               ret(4, 64, 128, (0.96, 0.99, 0.999, 0.9995), rot(10000.0, 32)), 1.3, 0.8), dense(384)),
         layer("parallel", par(attn(4, 4, 64, 64, 0.12, 200, rot(50000.0, 64)),
@@ -131,7 +131,7 @@ def draw_case(seed: int) -> dict:
 
     def draw_rot(dim):
         dims = r.choice([d for d in (2, 4, 8, 16, 32, 64) if d <= dim])
-        sc = r.choice([None, None, (r.choice([2.0, 8.0, 40.0]), r.choice([64, 1024]), r.choice([4.0, 32.0]), r.choice([0.5, 1.0]))])
+        sc = r.choice([None, None, (r.choice([2.0, 6.0, 40.0]), r.choice([64, 1024]), r.choice([4.0, 24.0]), r.choice([0.5, 1.5]))])
         return rot(r.choice([100.0, 1e4, 300000.0]), dims, sc)
 
     def draw_attn():
