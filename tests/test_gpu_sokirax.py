@@ -371,7 +371,7 @@ def _case(name, dtype):
     return name + "B" if dtype == "bfloat16" and name + "B" in CASES else name
 
 
-@pytest.mark.parametrize("name", ["S", "ONE", "W"])
+@pytest.mark.parametrize("name", ["S", "ONE", "W", "F"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompts_and_every_layer(tmp_path_factory, name, dtype):
     from gogguf_b200.engine import LayerTaps, StepEntry
@@ -403,7 +403,7 @@ def test_whole_prompts_and_every_layer(tmp_path_factory, name, dtype):
 
 
 @pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("ONE", "float32"), ("W", "float32"),
-                                        ("W", "bfloat16")])
+                                        ("W", "bfloat16"), ("F", "bfloat16"), ("F", "float32")])
 def test_portions_and_decoding_equal_the_whole_prompt(tmp_path_factory, name, dtype):
     name = _case(name, dtype)
     folder = make_folder(tmp_path_factory.getbasetemp(), name, dtype)
@@ -423,7 +423,8 @@ def test_portions_and_decoding_equal_the_whole_prompt(tmp_path_factory, name, dt
     assert close(got, want[:90], dtype, routed=False), err
 
 
-@pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("W", "bfloat16"), ("ONE", "float32")])
+@pytest.mark.parametrize("name,dtype", [("S", "float32"), ("S", "bfloat16"), ("W", "bfloat16"), ("ONE", "float32"),
+                                        ("F", "bfloat16")])
 def test_unequal_batches_reused_slots_and_pages(tmp_path_factory, name, dtype):
     """Requests of different lengths in one batch, decoded together while the short ones leave; the slots, pages and
     states they give back are taken by the next batch (the cache is sized so that it has to reuse them)."""
