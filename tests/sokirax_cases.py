@@ -104,11 +104,11 @@ def every_expert(cfg: dict) -> dict:
 CASE_F = dict(
     architecture="Sokirax", vocab=307, width=256, norm=dict(eps=1e-5),
     layers=[
-        layer("attention", attn(4, 2, 128, 128, 0.1, 100, rot(30000.0, 128, (5.0, 128, 20.0, 2.0))), dense(320)),
+        layer("attention", attn(6, 3, 128, 128, 0.1, 100, rot(30000.0, 128, (5.0, 128, 20.0, 2.0))), dense(320)),
         layer("parallel", par(attn(4, 1, 64, 64, 0.15, 70, rot(2000.0, 64, (3.0, 64, 8.0, 1.0))),
                               ret(2, 32, 96, (0.97, 0.999), rot(2000.0, 32, (3.0, 64, 8.0, 1.0))), 0.9, 1.4), dense(192)),
         layer("attention", attn(32, 1, 64, 64, 0.12, None, rot(10000.0, 64)), None),
-        layer("attention", attn(4, 2, 128, 128, 0.1, 100, rot(30000.0, 128, (5.0, 128, 20.0, 2.0))), dense(320), weights_of=0),
+        layer("attention", attn(6, 3, 128, 128, 0.1, 100, rot(30000.0, 128, (5.0, 128, 20.0, 2.0))), dense(320), weights_of=0),
     ])
 CASES = {"S": (CASE_S, 3), "ONE": (CASE_ONE, 4), "W": (CASE_W, 6), "F": (CASE_F, 8)}
 CASES.update({"SB": (every_expert(CASE_S), 3), "WB": (every_expert(CASE_W), 6)})
