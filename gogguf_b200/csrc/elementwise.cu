@@ -496,15 +496,15 @@ GG_API gg_qkv_prep(const void* qkv, int dtype, void* q_out, const float* qw, con
 // With xhat and ssq it also leaves what a product with a folded norm reads of the updated row: its bfloat16 copy
 // and the sums of its squares over blocks of 128 columns (see row_stats_kernel), so the norm before the next
 // part needs no kernel of its own.
-__global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float* y, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, float* y, const float* __restrict__ w,
                                                           int H, float eps, bf16* __restrict__ xhat,
-                                                          float* __restrict__ ssq, int parts) {
+                                                          float* __restrict__ ssq, int parts, int zero_y) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
     extern __shared__ float psum[];          // [parts][4]: a 128-column block is four warps' 32 columns
     const size_t r = blockIdx.x;
-    const float* yr = y + r * H;
+    float* yr = y + r * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
@@ -516,6 +516,7 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float*
         if (i < H) {
             v = x[r * H + i] + yr[i] * f * w[i];
             x[r * H + i] = v;
+            if (zero_y) yr[i] = 0.f;
             if (xhat != nullptr) xhat[r * H + i] = __float2bfloat16_rn(v);
         }
         if (ssq != nullptr) {
@@ -533,14 +534,14 @@ __global__ void __launch_bounds__(256) rmsnorm_add_kernel(float* x, const float*
 
 // The same with 16-byte accesses (H a multiple of 4, rows on 16-byte boundaries): a thread owns four columns, a
 // warp the 128 columns of one block of the sums of squares, so those need no shared memory.
-__global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, const float* y, const float* __restrict__ w,
+__global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, float* y, const float* __restrict__ w,
                                                                int H, float eps, bf16* __restrict__ xhat,
-                                                               float* __restrict__ ssq, int parts) {
+                                                               float* __restrict__ ssq, int parts, int zero_y) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[33];
     const size_t r = blockIdx.x;
-    const float4* yr = reinterpret_cast<const float4*>(y + r * H);
+    float4* yr = reinterpret_cast<float4*>(y + r * H);
     const float4* wr = reinterpret_cast<const float4*>(w);
     float4* xr = reinterpret_cast<float4*>(x + r * H);
     const int n4 = H >> 2;
@@ -560,6 +561,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, const f
             float4 v;
             v.x = a.x + b.x * f * c.x; v.y = a.y + b.y * f * c.y; v.z = a.z + b.z * f * c.z; v.w = a.w + b.w * f * c.w;
             xr[i] = v;
+            if (zero_y) yr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (xhat != nullptr) {
                 __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
                 *reinterpret_cast<uint2*>(xhat + r * H + 4 * (size_t)i) =
@@ -575,9 +577,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_add_vec_kernel(float* x, const f
     }
 }
 
-// xhat (bfloat16 [rows, H]) and ssq (float32 [rows, ceil(H / 128)]) may both be null.
-GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H, float eps, void* xhat, float* ssq,
-                      cudaStream_t stream) {
+// xhat (bfloat16 [rows, H]) and ssq (float32 [rows, ceil(H / 128)]) may both be null.  zero_y != 0: y is left
+// zeroed (the buffer the next part of the block adds its output into, without a fill of its own).
+GG_API gg_rmsnorm_add(float* x, float* y, const float* w, int rows, int H, float eps, void* xhat, float* ssq,
+                      int zero_y, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0 || (xhat == nullptr) != (ssq == nullptr)) return GG_ERR_ARG;
     const int parts = (H + 127) / 128;
@@ -585,13 +588,13 @@ GG_API gg_rmsnorm_add(float* x, const float* y, const float* w, int rows, int H,
         // few rows (decode steps): as many threads as the row has groups of four columns, up to 1,024
         int threads = ((H >> 2) + 31) / 32 * 32;
         if (threads > 1024 || rows >= 512) threads = threads > 256 ? 256 : threads;
-        gg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts);
+        gg_launch(rmsnorm_add_vec_kernel, dim3(rows), dim3(threads), 0, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y);
         return gg_last_error();
     }
     // (a block of 128 columns whose tail lies beyond H gets zeros from the warps that have no column)
     const size_t smem = ssq != nullptr ? ((size_t)(parts + 1) * 4) * sizeof(float) : 0;
     if (smem > 48 * 1024) return GG_ERR_ARG;
-    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), smem, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts);
+    gg_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), smem, stream, 1, x, y, w, H, eps, (bf16*)xhat, ssq, parts, zero_y);
     return gg_last_error();
 }
 

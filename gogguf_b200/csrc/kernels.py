@@ -132,10 +132,10 @@ def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Te
 
 
 def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
-                xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None) -> None:
+                xhat: Optional[torch.Tensor] = None, ssq: Optional[torch.Tensor] = None, zero_y: bool = False) -> None:
     """x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight, all float32.  With `xhat` (bfloat16 like x) and `ssq`
     (float32 [rows, ceil(H / 128)]) the updated rows' bfloat16 copy and sums of squares per 128 columns are left too
-    (what `row_stats` makes)."""
+    (what `row_stats` makes).  zero_y: y is left zeroed."""
     _need(x, torch.float32, "x")
     _need(y, torch.float32, "y")
     _need(weight, torch.float32, "norm weight")
@@ -150,7 +150,7 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
         if xhat.numel() != x.numel() or ssq.numel() != (x.numel() // H) * ((H + 127) // 128):
             raise KernelError("rmsnorm_add: shapes of xhat / ssq disagree")
     kernel("elementwise", "gg_rmsnorm_add")(_p(x), _p(y), _p(weight), x.numel() // H, H, float(eps), _p(xhat), _p(ssq),
-                                             _stream())
+                                             int(zero_y), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, n_tokens: int, inter: int) -> None:

@@ -86,6 +86,7 @@ class ParallelBlock:
             return
         buf = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
         buf.zero_()
+        ctx.shared.pop("block_part_out_zeroed", None)      # (a mark other arrangements keep on this buffer)
         call(buf)
         K.residual_axpy(x, buf, self.mult)
 
@@ -109,6 +110,7 @@ class SandwichNormBlock:
     optional_roles = ("feed_forward", "feed_forward_norm", "feed_forward_post_norm")
     keeps_row_stats = True      # its statistics are its own (see `forward`); it clears and sets `fresh` itself
     STATS = "sandwich_row_stats"
+    ZEROED = "block_part_out_zeroed"      # ctx.shared: address of the parts' output buffer while it is known to hold zeros
 
     def __init__(self, spec: BlockSpec, parts: Dict[str, object], rt: Runtime):
         self.parts = dict(parts)
@@ -134,15 +136,19 @@ class SandwichNormBlock:
             h = ctx.ws.get("block_normed", tuple(x.shape), self.rt.dtype)
             pre.forward(x, h)
         y = ctx.ws.get("block_part_out", tuple(x.shape), torch.float32)
-        y.zero_()
+        # the norm-and-add kernel leaves the buffer zeroed for the part that comes next; only the step's first part
+        # (or one that follows a block of another make, which says so by dropping the mark) pays for a fill
+        if ctx.shared.get(self.ZEROED) != y.data_ptr():
+            y.zero_()
         call(h, y)
         if stats is not None and emit:
-            K.rmsnorm_add(x, y, post.weight, post.eps, xhat=stats.xhat, ssq=stats.ssq)
+            K.rmsnorm_add(x, y, post.weight, post.eps, xhat=stats.xhat, ssq=stats.ssq, zero_y=True)
             stats.fresh = True
         else:
-            K.rmsnorm_add(x, y, post.weight, post.eps)
+            K.rmsnorm_add(x, y, post.weight, post.eps, zero_y=True)
             if stats is not None:
                 stats.fresh = False
+        ctx.shared[self.ZEROED] = y.data_ptr()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache, writes_cache: bool) -> None:
         # The statistics live under a key of this arrangement's own: a part's last product writes into the part's
