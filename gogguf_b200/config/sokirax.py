@@ -255,17 +255,22 @@ class SokiraxConfig:
                 raise ConfigError(f"sokirax config: {where}.type={kind!r} is not known (attention, parallel)")
             mlp = ld.get("mlp")
             src = ld.get("weights_of")
-            if src is not None:
-                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i):
-                    raise ConfigError(f"sokirax config: {where}.weights_of={src!r} must name an earlier layer")
-                if layers[src].weights_of is not None:
-                    raise ConfigError(f"sokirax config: {where}.weights_of={src} names a layer without tensors")
-            layer = SokiraxLayer(type=kind, mixer=mixer, weights_of=src,
-                                 mlp=None if mlp is None else FeedForwardConfig.from_dict(mlp, where + ".mlp"))
-            if src is not None and (layer.type, layer.mixer, layer.mlp) != (
-                    layers[src].type, layers[src].mixer, layers[src].mlp):
-                raise ConfigError(f"sokirax config: {where} uses the tensors of layer {src} but describes other sizes")
-            layers.append(layer)
+            if src is not None and (isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < len(raw))
+                                    or src == i):
+                raise ConfigError(f"sokirax config: {where}.weights_of={src!r} must name another layer")
+            layers.append(SokiraxLayer(type=kind, mixer=mixer, weights_of=src,
+                                       mlp=None if mlp is None else FeedForwardConfig.from_dict(mlp, where + ".mlp")))
+        for i, layer in enumerate(layers):
+            # the layer whose tensors are used (before or after this one) must have tensors, and the same parts:
+            # both run one set of built parts, each with a cache and state of its own
+            if layer.weights_of is None:
+                continue
+            src = layers[layer.weights_of]
+            if src.weights_of is not None:
+                raise ConfigError(f"sokirax config: layers[{i}].weights_of={layer.weights_of} names a layer without tensors")
+            if (layer.type, layer.mixer, layer.mlp) != (src.type, src.mixer, src.mlp):
+                raise ConfigError(f"sokirax config: layers[{i}] uses the tensors of layer {layer.weights_of} "
+                                  "but describes other sizes")
         eps = _number(_need(d, "norm", "config"), "eps", "norm")
         if not eps > 0:
             raise ConfigError(f"sokirax config: norm.eps must be > 0, got {eps}")
@@ -346,8 +351,7 @@ class SokiraxConfig:
             return PartSpec(kind="rmsnorm", prefix=p, params=dict(size=W, eps=eps, tensor=name))
 
         for i, l in enumerate(self.layers):
-            if l.weights_of is not None:        # the same parts once more, with a cache and state of its own
-                schedule.append(ScheduleEntry(block=block_of[l.weights_of]))
+            if l.weights_of is not None:
                 continue
             p = f"l{i}."
             if l.type == "attention":
@@ -378,7 +382,9 @@ class SokiraxConfig:
                              feed_forward_post_norm=norm(p, "norm2b"))
             block_of[i] = len(blocks)
             blocks.append(BlockSpec("sandwich_norm", parts))
-            schedule.append(ScheduleEntry(block=block_of[i]))
+        # a layer that names another layer's tensors is that layer's block once more, with a cache and state of its own
+        for i, l in enumerate(self.layers):
+            schedule.append(ScheduleEntry(block=block_of[i if l.weights_of is None else l.weights_of]))
         spec = ModelSpec(
             architecture="Sokirax", vocab_size=self.vocab, hidden_size=W, max_positions=MAX_POSITIONS,
             blocks=tuple(blocks), schedule=tuple(schedule),

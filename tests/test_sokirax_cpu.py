@@ -55,7 +55,8 @@ def test_shapes_follow_the_configuration():
     lambda d: d["layers"][1]["mixer"].update(heads=3),                         # not a multiple of kv_heads
     lambda d: d["layers"][0]["mixer"]["right"].update(decay=[0.5]),            # one decay per head
     lambda d: d["layers"][1]["mixer"]["rot"].update(dims=7),
-    lambda d: d["layers"][2].update(weights_of=2),                             # not an earlier layer
+    lambda d: d["layers"][2].update(weights_of=2),                             # itself
+    lambda d: d["layers"][2].update(weights_of=9),                             # no such layer
     lambda d: d["layers"][4].update(weights_of=2),                             # a layer without tensors
     lambda d: d["layers"][4].update(weights_of=3),                             # other sizes than its source
     lambda d: d["layers"][0]["mlp"]["router"].update(top=9),
@@ -143,3 +144,15 @@ def test_drawn_configurations_parse_and_declare_their_tensors(seed):
     cfg = _cfg(d)
     assert cfg.to_dict() == d
     assert expected_tensors(cfg.to_spec())
+
+
+def test_a_layer_may_run_the_tensors_of_a_later_one():
+    from gogguf_b200.engine.model import expected_tensors
+    d = copy.deepcopy(CASES["S"][0])
+    first, third = d["layers"][0], d["layers"][2]
+    first["weights_of"] = 2
+    del third["weights_of"]
+    spec = _cfg(d).to_spec()
+    assert [e.block for e in spec.schedule] == [1, 0, 1, 2, 0]
+    names = set(expected_tensors(spec))
+    assert "l2.mix.left.sink" in names and not any(n.startswith("l0.") for n in names)
