@@ -727,3 +727,23 @@ def test_trace_replay_through_the_program(tmp_path_factory, tmp_path, name, dtyp
         tr.close()
     err = rel_err(torch.cat(got_rows), torch.cat(want_rows))
     assert close(torch.cat(got_rows), torch.cat(want_rows), dtype), err
+
+
+def test_a_layer_that_runs_the_tensors_of_a_later_one(tmp_path):
+    """The first layer names the third one's tensors: one set of parts, two runs, each with its cache and state."""
+    import copy
+    from gogguf_b200.config import config_from_dict
+    from gogguf_b200.engine.model import write_random_model
+    d = copy.deepcopy(CASES["S"][0])
+    d["layers"][0]["weights_of"] = 2
+    del d["layers"][2]["weights_of"]
+    folder = os.path.join(str(tmp_path), "later")
+    write_random_model(config_from_dict(d), 5, folder, dtype="float32", std=0.12, norm_std=0.1)
+    cfg, w = read_folder(folder)
+    assert "l2.mix.left.q" in w and not any(k.startswith("l0.") for k in w)
+    tokens = random_tokens(cfg["vocab"], 140, seed=4)
+    want = plain_logits(cfg, w, tokens)
+    model, cache, st = load(folder, "float32")
+    for cuts in ([140], [70, 3]):
+        got = run_cut(st, cache, tokens, cuts)
+        assert close(got, want, "float32", own32=plain.forward(cfg, w, tokens, torch.float32)), (cuts, rel_err(got, want))
